@@ -1,0 +1,320 @@
+#!/usr/bin/env python
+"""Benchmark of the fused 4-bit AdamW step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" is one optimizer step over the whole parameter list of the workload.  At N = 1 the
+workload is the Llama-7B-shaped parameter set (bf16 parameters and gradients, per-tensor gradient
+sigma log-uniform in [1e-5, 1e-2], 0.1 % of entries x100); at N > 1 the Llama-13B-shaped set with the
+optimizer state sharded over the ranks and an all-gather of the updated parameters.  All data is
+synthetic and seeded.  Rank 0 prints one JSON line.
+
+`value`      Gparams/s with everything resident in HBM, device time over exactly K steps.
+`e2e`        the same metric through the public optimizer class with the step's input (the gradients)
+             copied from pinned host memory inside the timed region and the step's status word read back.
+`roofline`   algorithmic HBM bytes of one step / device time of one step, against the measured copy peak.
+`cpu_baseline` the CPU oracle (C form, all host threads) on a bounded sample of the same workload.
+`--impl reference` times the reference's CPU path (its torch-operator restatement, the oracle) instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from quantfour_adamw_cuda_b200 import shapes as S  # noqa: E402
+
+HP = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.t0, self.t1 = index, None, 0.0, 0.0
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # the busiest half of the samples stands for "under load" (the sampler also sees the idle edges)
+        load = sorted(sm)[len(sm) // 2:] if sm else []
+        return {"sm_mhz": statistics.median(load) if load else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def synth_tensor(shape, sigma, gen, device, dtype=torch.bfloat16, outliers=True):
+    x = torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * sigma
+    if outliers:
+        mask = torch.rand(shape, generator=gen, device=device) < 1e-3
+        x = torch.where(mask, x * 100, x)
+    return x.to(dtype)
+
+
+def sigmas(n, seed=1234):
+    g = torch.Generator().manual_seed(seed)
+    return (10 ** torch.empty(n).uniform_(-5, -2, generator=g)).tolist()
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU legs (oracle)
+# ------------------------------------------------------------------------------------------------
+
+def cpu_sample_shapes(workload: str):
+    """Bounded sample of the workload: one decoder layer's nine tensors (Llama shapes) or the first
+    transformer block plus the position table (GPT-2 shape)."""
+    sh = S.WORKLOADS[workload]()
+    if workload.startswith("llama"):
+        return sh[1:10], "one decoder layer (4 attention + 3 MLP matrices + 2 norm vectors), bf16, warm state"
+    return sh[1:14], "position table + first transformer block, bf16, warm state"
+
+
+def run_cpu(workload: str, form: str, steps: int, warmup: int, budget_s: float = 25.0):
+    """Time the CPU oracle on the bounded sample.  form: 'c' (plain C, OpenMP) or 'torch' (the
+    reference's torch operators).  Returns (Gparams/s, cores, seconds per step, sample text)."""
+    from oracle import c_oracle, torch_oracle
+    shapes, text = cpu_sample_shapes(workload)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    c_oracle.set_threads(cores)
+    step_fn = c_oracle.step_tensor if form == "c" else torch_oracle.step_tensor
+    gen = torch.Generator().manual_seed(0)
+    sig = sigmas(len(shapes))
+    params = [synth_tensor(s, 0.02, gen, "cpu", outliers=False) for s in shapes]
+    grads = [synth_tensor(s, sg, gen, "cpu") for s, sg in zip(shapes, sig)]
+    states = [torch_oracle.TensorState.zeros(s) for s in shapes]
+    hp = (HP["lr"], HP["betas"][0], HP["betas"][1], HP["eps"], HP["weight_decay"])
+
+    def one():
+        for p, g, st in zip(params, grads, states):
+            step_fn(p, g, st, *hp)
+
+    t0 = time.perf_counter()
+    one()
+    first = time.perf_counter() - t0
+    warm = max(1, min(warmup, int(budget_s * 0.3 / max(first, 1e-3))))
+    for _ in range(warm - 1):
+        one()
+    k = max(1, min(steps, int(budget_s * 0.7 / max(first, 1e-3))))
+    t0 = time.perf_counter()
+    for _ in range(k):
+        one()
+    dt = (time.perf_counter() - t0) / k
+    n = S.numel(shapes)
+    return n / dt / 1e9, cores, dt, f"{text}; {n} params, {k} timed steps after {warm} warm-up"
+
+
+def reference_arm(args):
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    workload = args.workload or ("llama7b" if args.gpus == 1 else "llama13b")
+    value, cores, dt, text = run_cpu(workload, "torch", args.steps, args.warmup, budget_s=120.0)
+    print(json.dumps({
+        "impl": "reference", "metric": "4-bit AdamW step throughput", "value": value, "unit": "Gparams/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload, "sample": text},
+        "cpu_baseline": {"value": value, "unit": "Gparams/s", "cores": cores, "kind": "port", "sample": text},
+        "e2e": {"value": value, "unit": "Gparams/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "the reference's pure-PyTorch path cannot complete a step (it stops itself); timed here is its "
+                "torch-operator restatement (oracle/torch_oracle.py) on all host threads",
+    }))
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm, one GPU
+# ------------------------------------------------------------------------------------------------
+
+def build_problem(shapes, device, seed=0, grad_sets=2):
+    gen = torch.Generator(device=device).manual_seed(seed)
+    sig = sigmas(len(shapes))
+    params = [torch.nn.Parameter(synth_tensor(s, 0.02, gen, device, outliers=False), requires_grad=False) for s in shapes]
+    grads = [[synth_tensor(s, sg, gen, device) for s, sg in zip(shapes, sig)] for _ in range(grad_sets)]
+    return params, grads
+
+
+def single_gpu(args):
+    import ctypes as C
+
+    import quantfour_adamw_cuda_b200 as qf
+    from quantfour_adamw_cuda_b200 import _lib
+
+    workload = args.workload or "llama7b"
+    shapes = S.WORKLOADS[workload]()
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    n_params = S.numel(shapes)
+    alg_bytes = S.algorithmic_bytes(shapes)
+    params, grads = build_problem(shapes, dev)
+    opt = qf.FourBitAdamW(params, **HP)
+
+    def set_grads(k):
+        for p, g in zip(params, grads[k % len(grads)]):
+            p.grad = g
+
+    # ---- warm-up through the public API (also builds the state and the descriptor table) ----------
+    for i in range(max(3, args.warmup)):
+        set_grads(i)
+        opt.step()
+    torch.cuda.synchronize(dev)
+
+    # ---- timed region: exactly K steps, device time -----------------------------------------------
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    time.sleep(0.3)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    torch.cuda.synchronize(dev)
+    ev[0].record()
+    for i in range(args.steps):
+        set_grads(i)
+        opt.step()
+        ev[i + 1].record()
+    torch.cuda.synchronize(dev)
+    total_ms = ev[0].elapsed_time(ev[-1])
+    per_step = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    clocks = sampler.stop()
+    ms_per_step = total_ms / args.steps
+    value = n_params / (ms_per_step * 1e-3) / 1e9
+
+    # ---- per-kernel split: the two halves of the step through the C ABI, events around each --------
+    L = _lib.lib()
+    plan = next(iter(opt._plans.values()))
+    stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    pre_ms = main_ms = 0.0
+    reps = min(args.steps, 10)
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    for i in range(reps):
+        for st in opt.state.values():
+            st["step"] += 1
+        h = (_lib.QfHyper * 1)(qf.make_hyper(HP["lr"], *HP["betas"], HP["eps"], HP["weight_decay"],
+                                             float(next(iter(opt.state.values()))["step"])))
+        a = (plan.descs, len(plan.descs), h, 1, plan.workspace.data_ptr(), plan.workspace.numel(), dev.index, stream)
+        e[0].record()
+        _lib.check(L.qf_step_pre(*a), "qf_step_pre")
+        e[1].record()
+        _lib.check(L.qf_step_main(*a), "qf_step_main")
+        e[2].record()
+        torch.cuda.synchronize(dev)
+        pre_ms += e[0].elapsed_time(e[1]) / reps
+        main_ms += e[1].elapsed_time(e[2]) / reps
+
+    # ---- end to end: gradients arrive from pinned host memory every step ----------------------------
+    e2e = None
+    if not args.no_e2e:
+        host = [g.cpu().pin_memory() for g in grads[0]]
+        h2d = sum(t.numel() * t.element_size() for t in host)
+        dst = grads[0]
+        k = max(1, min(args.steps, 5))
+        for p, g in zip(params, dst):
+            p.grad = g
+
+        def e2e_step():
+            for hsrc, d in zip(host, dst):
+                d.copy_(hsrc, non_blocking=True)
+            opt.step()
+            return opt.nonfinite_seen()   # device -> host read of the step's status word; synchronises
+
+        e2e_step()
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        for _ in range(k):
+            e2e_step()
+        dt = (time.perf_counter() - t0) / k
+        e2e = {"value": n_params / dt / 1e9, "unit": "Gparams/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+               "ms_per_step": dt * 1e3, "steps": k}
+        del host
+
+    peak, peak_kind = measured_peak()
+    achieved = alg_bytes / (ms_per_step * 1e-3) / 1e9
+    out = {
+        "metric": "4-bit AdamW step throughput", "value": value, "unit": "Gparams/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload, "tensors": len(shapes), "params": n_params, "param_dtype": "bf16",
+                   "state": "4-bit m (block-128) + 4-bit v (rank-1 / block-128), fp32 for numel <= 4096",
+                   "l2": "inputs (%.1f GB per step) are far larger than L2" % (alg_bytes / 1e9),
+                   "ms_per_step_min": min(per_step), "ms_per_step_max": max(per_step)},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
+                     "algorithmic_bytes_per_step": alg_bytes, "kernels_ms": {"pre": pre_ms, "main": main_ms},
+                     "note": "whole step (clear + pre + main + roll kernels) over algorithmic bytes"},
+        "e2e": e2e, "gpu_launches": 4 * args.steps, "clocks": clocks,
+    }
+    if not args.no_cpu:
+        v, cores, dt, text = run_cpu(workload, "c", 3, 1)
+        out["cpu_baseline"] = {"value": v, "unit": "Gparams/s", "cores": cores, "kind": "port", "sample": text,
+                               "form": "plain-C oracle with OpenMP"}
+    print(json.dumps(out))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, choices=[None, *S.WORKLOADS])
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU arm")
+    if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        return single_gpu(args)
+    from quantfour_adamw_cuda_b200 import zero1_bench
+    return zero1_bench.run(args, HP)
+
+
+if __name__ == "__main__":
+    main()

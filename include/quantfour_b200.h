@@ -1,0 +1,167 @@
+/*
+ * quantfour_b200.h -- C ABI of libquantfour_b200.so: the fused 4-bit AdamW optimizer step for
+ * NVIDIA B200 (sm_100a).
+ *
+ * This library stands where the reference project's pybind11 extension `quantfour_cuda` stands
+ * (optim/cuda_fused_interface.cc:1-69, kernels in optim/cuda_adamw_kernels.cu).  It has no torch
+ * or ATen type in any signature: device pointers, sizes, a device ordinal and a CUDA stream handle.
+ * Every function returns a QfStatus; on failure qf_last_error() gives a message for the calling
+ * thread.  All launches are asynchronous on the stream that is passed in; nothing synchronises the
+ * device except qf_read_status().  The library allocates no device memory: the caller owns every
+ * buffer, the workspace included.
+ *
+ * Data layout (all buffers contiguous, in device memory):
+ *   parameters / gradients ... fp32 or bf16, `numel` elements, 16-byte aligned
+ *   4-bit codes .............. one byte per two elements, element 2j in bits 0-3 and element 2j+1
+ *                              in bits 4-7 of byte j; ceil(numel/2) bytes, 4-byte aligned
+ *   first-moment scales ...... fp32, one per 128 consecutive (flattened) elements
+ *   second-moment scales ..... QF_KIND_BLOCK: fp32, one per 128 elements;
+ *                              QF_KIND_RANK1: fp32 row maxima [rows] and column maxima [cols];
+ *                              the scale of element (i, j) is min(row[i], col[j])
+ *   QF_KIND_FP32 ............. both moments are plain fp32 arrays of `numel` elements
+ */
+#ifndef QUANTFOUR_B200_H
+#define QUANTFOUR_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QF_ABI_VERSION 1
+#define QF_BLOCK 128        /* elements per quantization block (optim/cuda_adamw_kernels.cu:431) */
+#define QF_MAX_HYPERS 16    /* hyper-parameter sets one launch can carry */
+
+typedef enum QfStatus {
+    QF_OK = 0,
+    QF_ERR_BAD_ARG = 1,      /* null pointer, misaligned buffer, negative size, bad enum ... */
+    QF_ERR_WORKSPACE = 2,    /* workspace missing or smaller than qf_workspace_bytes()      */
+    QF_ERR_CUDA = 3,         /* a CUDA runtime call or a launch failed                      */
+    QF_ERR_NO_DEVICE = 4     /* no usable CUDA device / driver                              */
+} QfStatus;
+
+typedef enum QfDtype { QF_F32 = 0, QF_BF16 = 1 } QfDtype;
+
+typedef enum QfKind {
+    QF_KIND_FP32 = 0,   /* moments kept in fp32 (tensors at or below the size threshold;
+                           the reference's kernel_cuda_single_tensor, cuda_adamw_kernels.cu:100-133) */
+    QF_KIND_BLOCK = 1,  /* both moments 4-bit with block-128 scales                               */
+    QF_KIND_RANK1 = 2   /* first moment block-128, second moment rank-1 (2-D tensors)             */
+} QfKind;
+
+/* Bits of the device status word (see qf_read_status). */
+#define QF_STATUS_NONFINITE 1u   /* a non-finite scale was produced (non-finite gradient or overflow) */
+
+/*
+ * Scalars of one optimizer step, derived by the host in double precision and rounded once to fp32
+ * (the reference derives them in fp32 inside its launcher, cuda_adamw_kernels.cu:435-440; its
+ * PyTorch path uses Python doubles, adamw_fourbit_triton.py:458-465 -- the latter is followed).
+ */
+typedef struct QfHyper {
+    float decay;     /* 1 - lr * weight_decay          */
+    float w1;        /* 1 - beta1                      */
+    float beta2;     /* beta2                          */
+    float w2;        /* 1 - beta2                      */
+    float eps;       /* eps                            */
+    float neg_step;  /* -(lr / (1 - beta1^step))       */
+    float bc2s;      /* sqrt(1 - beta2^step)           */
+    float pad;
+} QfHyper;
+
+/* One tensor of a multi-tensor step.  Replaces the per-tensor argument list of the reference's
+ * fused_4bit(p, g, exp, sq, exp_scale, sq_scale, ...) (cuda_fused_interface.cc:19-25). */
+typedef struct QfTensorDesc {
+    void* p;              /* parameters, updated in place                                        */
+    const void* g;        /* gradients, same dtype as p                                          */
+    void* m;              /* first moment: codes (uint8) or, for QF_KIND_FP32, fp32 values       */
+    void* v;              /* second moment: codes (uint8) or fp32 values                         */
+    float* m_scale;       /* [ceil(numel/128)]; unused for QF_KIND_FP32                          */
+    float* v_scale;       /* BLOCK: [ceil(numel/128)]; RANK1: row maxima [rows]; in/out          */
+    float* v_col;         /* RANK1: column maxima [cols]; in/out                                 */
+    float* v_row_new;     /* RANK1: scratch [rows] the step accumulates the new row maxima in    */
+    float* v_col_new;     /* RANK1: scratch [cols] for the new column maxima                     */
+    int64_t numel;
+    int64_t rows;         /* RANK1 only; rows * cols == numel                                    */
+    int64_t cols;
+    int32_t kind;         /* QfKind                                                              */
+    int32_t dtype;        /* QfDtype of p and g                                                  */
+    int32_t hyper;        /* index into the hyper-parameter array of the call                    */
+    int32_t reserved;
+} QfTensorDesc;
+
+int qf_abi_version(void);
+
+/* Message of the last failure on the calling thread ("" if none). */
+const char* qf_last_error(void);
+
+/* Bytes of device workspace a step over n_tensors tensors needs.  The workspace holds the device
+ * copy of the descriptor table and the status word; the library treats its contents as its own
+ * between calls (it skips the upload when the table has not changed). */
+size_t qf_workspace_bytes(int n_tensors);
+
+/*
+ * One optimizer step over a ragged list of tensors: dequantize both moments, AdamW update with
+ * decoupled weight decay, new scales, requantize, pack.  Replaces one call of the reference's
+ * fused_4bit / fused_single_tensor per tensor (cuda_fused_interface.cc:19-64,
+ * cuda_adamw_kernels.cu:136-164, :422-469; driver loop optim/fused_quantfour.py:171-292).
+ *
+ * `descs` and `hypers` are host arrays.  For RANK1 tensors the call (1) clears v_row_new/v_col_new,
+ * (2) accumulates the new maxima, (3) updates and requantizes using the old maxima for dequantize
+ * and the new ones for quantize, (4) copies the new maxima into v_scale/v_col.
+ */
+int qf_step_multi(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers,
+                  void* workspace, size_t workspace_bytes, int device, void* stream);
+
+/* The two halves of qf_step_multi, for callers that must combine the new column maxima of a tensor
+ * split by rows across devices (element-wise max of v_col_new over the devices that share it)
+ * between them.  qf_step_pre does (1)-(2), qf_step_main does (3)-(4). No counterpart in the
+ * reference, which has no sharding. */
+int qf_step_pre(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers,
+                void* workspace, size_t workspace_bytes, int device, void* stream);
+int qf_step_main(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers,
+                 void* workspace, size_t workspace_bytes, int device, void* stream);
+
+/* Synchronise `stream`, read the status word kept in `workspace` into *status (QF_STATUS_* bits)
+ * and clear it. */
+int qf_read_status(void* workspace, int device, void* stream, uint32_t* status);
+
+/*
+ * Single-tensor entry points with the reference's argument order
+ * (fused_4bit: cuda_fused_interface.cc:19-25; fused_single_tensor: :49-60).  Scalars are doubles;
+ * `step` is the step count after the increment.  In qf_fused_4bit both moments use block-128
+ * scales (exp_scale, sq_scale: [ceil(numel/128)]), which is what the reference's signature can
+ * express; rank-1 second moments go through qf_step_multi.
+ */
+int qf_fused_4bit(void* p, const void* g, void* exp, void* sq, float* exp_scale, float* sq_scale,
+                  int64_t numel, int dtype, double beta1, double beta2, double lr, double weight_decay,
+                  double eps, double step, int device, void* stream);
+int qf_fused_single_tensor(void* p, const void* g, float* exp_avg, float* exp_avg_sq, int64_t numel,
+                           int dtype, double beta1, double beta2, double lr, double weight_decay,
+                           double eps, double step, int device, void* stream);
+
+/* Derive the scalars of a step the way the PyTorch path of the reference does
+ * (adamw_fourbit_triton.py:415, :458-465). */
+void qf_make_hyper(double lr, double beta1, double beta2, double eps, double weight_decay, double step,
+                   QfHyper* out);
+
+/*
+ * Stand-alone quantize / dequantize (the pieces of the step; the reference describes them at
+ * adamw_fourbit_triton.py:556-630, :801-863 and :497-546 but ships no kernel for them).
+ * `map`: 0 = first-moment map (signed, dynamic exponent), 1 = second-moment map (unsigned,
+ * linear, zero excluded).  Inputs / outputs are fp32.
+ */
+int qf_quantize_block(const float* x, int64_t numel, int map, uint8_t* codes, float* scales,
+                      int device, void* stream);
+int qf_dequantize_block(const uint8_t* codes, const float* scales, int64_t numel, int map, float* out,
+                        int device, void* stream);
+int qf_quantize_rank1(const float* v, int64_t rows, int64_t cols, uint8_t* codes, float* row_max,
+                      float* col_max, int device, void* stream);
+int qf_dequantize_rank1(const uint8_t* codes, const float* row_max, const float* col_max, int64_t rows,
+                        int64_t cols, float* out, int device, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QUANTFOUR_B200_H */

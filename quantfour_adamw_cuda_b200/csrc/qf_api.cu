@@ -1,0 +1,411 @@
+// Host side of libquantfour_b200.so: argument validation, the device descriptor table and the
+// launches.  The exported functions are declared and documented in include/quantfour_b200.h.
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "qf_kernels.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+#define QF_CUDA(call)                                                                          \
+    do {                                                                                       \
+        cudaError_t e_ = (call);                                                               \
+        if (e_ != cudaSuccess)                                                                 \
+            return fail(e_ == cudaErrorNoDevice || e_ == cudaErrorInsufficientDriver ? QF_ERR_NO_DEVICE : QF_ERR_CUDA, \
+                        "%s failed: %s", #call, cudaGetErrorString(e_));                      \
+    } while (0)
+
+constexpr size_t kStatusBytes = 256;  // head of the workspace: status word, then padding
+
+size_t table_bytes(int n) { return static_cast<size_t>(n) * sizeof(qf::DevTensor) + 2 * (static_cast<size_t>(n) + 1) * 8; }
+size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+int64_t flat_items(int64_t numel) {
+    const int64_t per = static_cast<int64_t>(qf::kPanelCols) * qf::kRowsPerItem;
+    return (numel + per - 1) / per;
+}
+
+// What the library remembers about a workspace: the table it last uploaded there and a pair of
+// pinned staging buffers so that an upload never has to wait for the stream.
+struct WsCache {
+    std::vector<char> last;
+    char* pinned[2] = {nullptr, nullptr};
+    cudaEvent_t ev[2] = {nullptr, nullptr};
+    size_t cap = 0;
+    int cur = 0;
+};
+std::mutex g_mu;
+std::unordered_map<uint64_t, WsCache> g_cache;
+
+struct Plan {
+    int n = 0;                    // tensors in the table (zero-size tensors dropped)
+    int64_t main_items = 0, pre_items = 0;
+    int n_rank1 = 0;
+    qf::DevTensor* d_tensors = nullptr;
+    int64_t* d_main_base = nullptr;
+    int64_t* d_pre_base = nullptr;
+    uint32_t* d_status = nullptr;
+};
+
+int build_plan(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* workspace, size_t workspace_bytes,
+               int device, cudaStream_t stream, Plan* plan) {
+    if (n_tensors < 0) return fail(QF_ERR_BAD_ARG, "n_tensors is negative");
+    if (n_tensors > 0 && !descs) return fail(QF_ERR_BAD_ARG, "descs is null");
+    if (n_hypers < 1 || n_hypers > QF_MAX_HYPERS)
+        return fail(QF_ERR_BAD_ARG, "n_hypers must be in 1..%d, got %d", QF_MAX_HYPERS, n_hypers);
+    if (!workspace || workspace_bytes < qf_workspace_bytes(n_tensors))
+        return fail(QF_ERR_WORKSPACE, "workspace of %zu bytes needed for %d tensors, got %zu", qf_workspace_bytes(n_tensors),
+                    n_tensors, workspace_bytes);
+    if (!aligned(workspace, 256)) return fail(QF_ERR_BAD_ARG, "workspace must be 256-byte aligned");
+
+    std::vector<qf::DevTensor> tab;
+    std::vector<int64_t> main_base{0}, pre_base{0};
+    tab.reserve(n_tensors);
+    int n_rank1 = 0;
+    for (int i = 0; i < n_tensors; ++i) {
+        const QfTensorDesc& d = descs[i];
+        if (d.numel < 0) return fail(QF_ERR_BAD_ARG, "tensor %d: negative numel", i);
+        if (d.numel == 0) continue;
+        if (d.dtype != QF_F32 && d.dtype != QF_BF16) return fail(QF_ERR_BAD_ARG, "tensor %d: bad dtype %d", i, d.dtype);
+        if (d.kind < QF_KIND_FP32 || d.kind > QF_KIND_RANK1) return fail(QF_ERR_BAD_ARG, "tensor %d: bad kind %d", i, d.kind);
+        if (d.hyper < 0 || d.hyper >= n_hypers) return fail(QF_ERR_BAD_ARG, "tensor %d: hyper index %d out of range", i, d.hyper);
+        if (!d.p || !d.g || !d.m || !d.v) return fail(QF_ERR_BAD_ARG, "tensor %d: null p/g/m/v pointer", i);
+        const size_t esz = d.dtype == QF_BF16 ? 2 : 4;
+        if (!aligned(d.p, esz) || !aligned(d.g, esz)) return fail(QF_ERR_BAD_ARG, "tensor %d: p/g not element-aligned", i);
+        qf::DevTensor t;
+        memset(&t, 0, sizeof t);
+        t.p = static_cast<char*>(d.p);
+        t.g = static_cast<const char*>(d.g);
+        t.m = static_cast<char*>(d.m);
+        t.v = static_cast<char*>(d.v);
+        t.numel = d.numel;
+        t.kind = d.kind;
+        t.dtype = d.dtype;
+        t.hyper = d.hyper;
+        bool vec = aligned(d.p, 16) && aligned(d.g, 16);
+        if (d.kind == QF_KIND_FP32) {
+            if (!aligned(d.m, 4) || !aligned(d.v, 4)) return fail(QF_ERR_BAD_ARG, "tensor %d: fp32 moments misaligned", i);
+            vec = vec && aligned(d.m, 16) && aligned(d.v, 16);
+        } else {
+            if (!d.m_scale || !d.v_scale) return fail(QF_ERR_BAD_ARG, "tensor %d: null scale pointer", i);
+            if (!aligned(d.m_scale, 4) || !aligned(d.v_scale, 4)) return fail(QF_ERR_BAD_ARG, "tensor %d: scales misaligned", i);
+            vec = vec && aligned(d.m, 4) && aligned(d.v, 4);
+            t.ms = d.m_scale;
+            t.vs = d.v_scale;
+        }
+        int64_t items = flat_items(d.numel);
+        if (d.kind == QF_KIND_RANK1) {
+            if (d.rows <= 0 || d.cols <= 0 || d.rows * d.cols != d.numel || d.rows > INT32_MAX || d.cols > INT32_MAX)
+                return fail(QF_ERR_BAD_ARG, "tensor %d: rows*cols must equal numel (rows=%lld cols=%lld numel=%lld)", i,
+                            (long long)d.rows, (long long)d.cols, (long long)d.numel);
+            if (!d.v_col || !d.v_row_new || !d.v_col_new) return fail(QF_ERR_BAD_ARG, "tensor %d: null rank-1 buffer", i);
+            if (!aligned(d.v_col, 4) || !aligned(d.v_row_new, 4) || !aligned(d.v_col_new, 4))
+                return fail(QF_ERR_BAD_ARG, "tensor %d: rank-1 buffers misaligned", i);
+            t.rows = static_cast<int32_t>(d.rows);
+            t.cols = static_cast<int32_t>(d.cols);
+            t.vcol = d.v_col;
+            t.vrow_new = d.v_row_new;
+            t.vcol_new = d.v_col_new;
+            const bool panel = vec && d.cols % qf::kPanelCols == 0 && aligned(d.v_col, 16) && aligned(d.v_col_new, 16);
+            if (panel) {
+                t.flags |= qf::kFlagPanel;
+                t.panels = static_cast<int32_t>(d.cols / qf::kPanelCols);
+                items = (d.rows + qf::kRowsPerItem - 1) / qf::kRowsPerItem * t.panels;
+            }
+            pre_base.push_back(pre_base.back() + items);
+            ++n_rank1;
+        } else {
+            pre_base.push_back(pre_base.back());
+        }
+        if (vec) t.flags |= qf::kFlagVec;
+        main_base.push_back(main_base.back() + items);
+        tab.push_back(t);
+    }
+    const int n = static_cast<int>(tab.size());
+    plan->n = n;
+    plan->n_rank1 = n_rank1;
+    plan->main_items = main_base.back();
+    plan->pre_items = pre_base.back();
+    char* ws = static_cast<char*>(workspace);
+    plan->d_status = reinterpret_cast<uint32_t*>(ws);
+    plan->d_tensors = reinterpret_cast<qf::DevTensor*>(ws + kStatusBytes);
+    plan->d_main_base = reinterpret_cast<int64_t*>(ws + kStatusBytes + static_cast<size_t>(n) * sizeof(qf::DevTensor));
+    plan->d_pre_base = plan->d_main_base + (n + 1);
+    if (n == 0) return QF_OK;
+
+    const size_t bytes = table_bytes(n);
+    std::vector<char> host(bytes);
+    memcpy(host.data(), tab.data(), static_cast<size_t>(n) * sizeof(qf::DevTensor));
+    memcpy(host.data() + static_cast<size_t>(n) * sizeof(qf::DevTensor), main_base.data(), (n + 1) * 8);
+    memcpy(host.data() + static_cast<size_t>(n) * sizeof(qf::DevTensor) + (n + 1) * 8, pre_base.data(), (n + 1) * 8);
+
+    std::lock_guard<std::mutex> lock(g_mu);
+    WsCache& c = g_cache[(static_cast<uint64_t>(device) << 56) ^ reinterpret_cast<uint64_t>(workspace)];
+    if (c.last.size() == bytes && memcmp(c.last.data(), host.data(), bytes) == 0) return QF_OK;
+    if (c.cap < bytes) {
+        for (int k = 0; k < 2; ++k) {
+            if (c.pinned[k]) cudaFreeHost(c.pinned[k]);
+            c.pinned[k] = nullptr;
+            QF_CUDA(cudaMallocHost(reinterpret_cast<void**>(&c.pinned[k]), round_up(bytes, 4096)));
+            if (!c.ev[k]) QF_CUDA(cudaEventCreateWithFlags(&c.ev[k], cudaEventDisableTiming));
+        }
+        c.cap = round_up(bytes, 4096);
+    }
+    const int k = c.cur ^ 1;
+    QF_CUDA(cudaEventSynchronize(c.ev[k]));  // the copy that last used this staging buffer has finished
+    memcpy(c.pinned[k], host.data(), bytes);
+    QF_CUDA(cudaMemcpyAsync(ws + kStatusBytes, c.pinned[k], bytes, cudaMemcpyHostToDevice, stream));
+    QF_CUDA(cudaEventRecord(c.ev[k], stream));
+    c.cur = k;
+    c.last.swap(host);
+    return QF_OK;
+}
+
+int grid_for(int64_t items, unsigned* grid) {
+    const int64_t ctas = (items + qf::kWarpsPerCta - 1) / qf::kWarpsPerCta;
+    if (ctas > 0x7fffffffLL) return fail(QF_ERR_BAD_ARG, "too many work items for one launch (%lld)", (long long)items);
+    *grid = static_cast<unsigned>(ctas);
+    return QF_OK;
+}
+
+int launch_pre(const Plan& pl, const qf::HyperPack& hp, cudaStream_t stream) {
+    if (pl.n_rank1 == 0) return QF_OK;
+    qf::rank1_roll_kernel<<<pl.n * qf::kRollSlices, qf::kThreads, 0, stream>>>(pl.d_tensors, pl.n, 0);
+    unsigned grid;
+    if (int rc = grid_for(pl.pre_items, &grid)) return rc;
+    qf::step_pre_kernel<<<grid, qf::kThreads, 0, stream>>>(pl.d_tensors, pl.d_pre_base, pl.n, hp, pl.d_status);
+    QF_CUDA(cudaGetLastError());
+    return QF_OK;
+}
+
+int launch_main(const Plan& pl, const qf::HyperPack& hp, cudaStream_t stream) {
+    if (pl.n == 0) return QF_OK;
+    unsigned grid;
+    if (int rc = grid_for(pl.main_items, &grid)) return rc;
+    qf::step_main_kernel<<<grid, qf::kThreads, 0, stream>>>(pl.d_tensors, pl.d_main_base, pl.n, hp, pl.d_status);
+    if (pl.n_rank1) qf::rank1_roll_kernel<<<pl.n * qf::kRollSlices, qf::kThreads, 0, stream>>>(pl.d_tensors, pl.n, 1);
+    QF_CUDA(cudaGetLastError());
+    return QF_OK;
+}
+
+int step_common(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,
+                size_t workspace_bytes, int device, void* stream, bool pre, bool main_) {
+    g_err[0] = 0;
+    if (!hypers) return fail(QF_ERR_BAD_ARG, "hypers is null");
+    QF_CUDA(cudaSetDevice(device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    Plan pl;
+    if (int rc = build_plan(descs, n_tensors, n_hypers, workspace, workspace_bytes, device, st, &pl)) return rc;
+    qf::HyperPack hp;
+    memset(&hp, 0, sizeof hp);
+    memcpy(hp.h, hypers, sizeof(QfHyper) * n_hypers);
+    if (pre)
+        if (int rc = launch_pre(pl, hp, st)) return rc;
+    if (main_)
+        if (int rc = launch_main(pl, hp, st)) return rc;
+    return QF_OK;
+}
+
+int check_1d(const void* a, const void* b, int64_t numel, const char* what) {
+    if (numel < 0) return fail(QF_ERR_BAD_ARG, "%s: negative numel", what);
+    if (numel > 0 && (!a || !b)) return fail(QF_ERR_BAD_ARG, "%s: null pointer", what);
+    return QF_OK;
+}
+
+unsigned flat_grid(int64_t numel) {
+    return static_cast<unsigned>((flat_items(numel) + qf::kWarpsPerCta - 1) / qf::kWarpsPerCta);
+}
+
+}  // namespace
+
+extern "C" {
+
+int qf_abi_version(void) { return QF_ABI_VERSION; }
+
+const char* qf_last_error(void) { return g_err; }
+
+size_t qf_workspace_bytes(int n_tensors) {
+    if (n_tensors < 0) n_tensors = 0;
+    return round_up(kStatusBytes + table_bytes(n_tensors), 256);
+}
+
+void qf_make_hyper(double lr, double beta1, double beta2, double eps, double weight_decay, double step, QfHyper* out) {
+    const double bc1 = 1.0 - std::pow(beta1, step);
+    const double bc2 = 1.0 - std::pow(beta2, step);
+    out->decay = static_cast<float>(1.0 - lr * weight_decay);
+    out->w1 = static_cast<float>(1.0 - beta1);
+    out->beta2 = static_cast<float>(beta2);
+    out->w2 = static_cast<float>(1.0 - beta2);
+    out->eps = static_cast<float>(eps);
+    out->neg_step = static_cast<float>(-(lr / bc1));
+    out->bc2s = static_cast<float>(std::sqrt(bc2));
+    out->pad = 0.0f;
+}
+
+int qf_step_multi(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,
+                  size_t workspace_bytes, int device, void* stream) {
+    return step_common(descs, n_tensors, hypers, n_hypers, workspace, workspace_bytes, device, stream, true, true);
+}
+
+int qf_step_pre(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,
+                size_t workspace_bytes, int device, void* stream) {
+    return step_common(descs, n_tensors, hypers, n_hypers, workspace, workspace_bytes, device, stream, true, false);
+}
+
+int qf_step_main(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,
+                 size_t workspace_bytes, int device, void* stream) {
+    return step_common(descs, n_tensors, hypers, n_hypers, workspace, workspace_bytes, device, stream, false, true);
+}
+
+int qf_read_status(void* workspace, int device, void* stream, uint32_t* status) {
+    g_err[0] = 0;
+    if (!workspace || !status) return fail(QF_ERR_BAD_ARG, "null workspace or status pointer");
+    QF_CUDA(cudaSetDevice(device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    QF_CUDA(cudaMemcpyAsync(status, workspace, sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
+    QF_CUDA(cudaMemsetAsync(workspace, 0, sizeof(uint32_t), st));
+    QF_CUDA(cudaStreamSynchronize(st));
+    return QF_OK;
+}
+
+int qf_fused_4bit(void* p, const void* g, void* exp, void* sq, float* exp_scale, float* sq_scale, int64_t numel,
+                  int dtype, double beta1, double beta2, double lr, double weight_decay, double eps, double step,
+                  int device, void* stream) {
+    g_err[0] = 0;
+    if (dtype != QF_F32 && dtype != QF_BF16) return fail(QF_ERR_BAD_ARG, "bad dtype %d", dtype);
+    if (numel < 0) return fail(QF_ERR_BAD_ARG, "negative numel");
+    if (numel == 0) return QF_OK;
+    if (!p || !g || !exp || !sq || !exp_scale || !sq_scale) return fail(QF_ERR_BAD_ARG, "null pointer");
+    QF_CUDA(cudaSetDevice(device));
+    qf::DevTensor t;
+    memset(&t, 0, sizeof t);
+    t.p = static_cast<char*>(p);
+    t.g = static_cast<const char*>(g);
+    t.m = static_cast<char*>(exp);
+    t.v = static_cast<char*>(sq);
+    t.ms = exp_scale;
+    t.vs = sq_scale;
+    t.numel = numel;
+    t.kind = QF_KIND_BLOCK;
+    t.dtype = dtype;
+    if (aligned(p, 16) && aligned(g, 16) && aligned(exp, 4) && aligned(sq, 4)) t.flags |= qf::kFlagVec;
+    QfHyper h;
+    qf_make_hyper(lr, beta1, beta2, eps, weight_decay, step, &h);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    qf::single_tensor_kernel<<<flat_grid(numel), qf::kThreads, 0, st>>>(t, h);
+    QF_CUDA(cudaGetLastError());
+    return QF_OK;
+}
+
+int qf_fused_single_tensor(void* p, const void* g, float* exp_avg, float* exp_avg_sq, int64_t numel, int dtype,
+                           double beta1, double beta2, double lr, double weight_decay, double eps, double step,
+                           int device, void* stream) {
+    g_err[0] = 0;
+    if (dtype != QF_F32 && dtype != QF_BF16) return fail(QF_ERR_BAD_ARG, "bad dtype %d", dtype);
+    if (numel < 0) return fail(QF_ERR_BAD_ARG, "negative numel");
+    if (numel == 0) return QF_OK;
+    if (!p || !g || !exp_avg || !exp_avg_sq) return fail(QF_ERR_BAD_ARG, "null pointer");
+    QF_CUDA(cudaSetDevice(device));
+    qf::DevTensor t;
+    memset(&t, 0, sizeof t);
+    t.p = static_cast<char*>(p);
+    t.g = static_cast<const char*>(g);
+    t.m = reinterpret_cast<char*>(exp_avg);
+    t.v = reinterpret_cast<char*>(exp_avg_sq);
+    t.numel = numel;
+    t.kind = QF_KIND_FP32;
+    t.dtype = dtype;
+    if (aligned(p, 16) && aligned(g, 16) && aligned(exp_avg, 16) && aligned(exp_avg_sq, 16)) t.flags |= qf::kFlagVec;
+    QfHyper h;
+    qf_make_hyper(lr, beta1, beta2, eps, weight_decay, step, &h);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    qf::single_tensor_kernel<<<flat_grid(numel), qf::kThreads, 0, st>>>(t, h);
+    QF_CUDA(cudaGetLastError());
+    return QF_OK;
+}
+
+int qf_quantize_block(const float* x, int64_t numel, int map, uint8_t* codes, float* scales, int device, void* stream) {
+    g_err[0] = 0;
+    if (int rc = check_1d(x, codes, numel, "qf_quantize_block")) return rc;
+    if (map != 0 && map != 1) return fail(QF_ERR_BAD_ARG, "map must be 0 or 1");
+    if (numel == 0) return QF_OK;
+    if (!scales) return fail(QF_ERR_BAD_ARG, "scales is null");
+    QF_CUDA(cudaSetDevice(device));
+    const int vec = aligned(x, 16) && aligned(codes, 4);
+    qf::quantize_block_kernel<<<flat_grid(numel), qf::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(x, numel, map, codes,
+                                                                                                      scales, vec);
+    QF_CUDA(cudaGetLastError());
+    return QF_OK;
+}
+
+int qf_dequantize_block(const uint8_t* codes, const float* scales, int64_t numel, int map, float* out, int device,
+                        void* stream) {
+    g_err[0] = 0;
+    if (int rc = check_1d(codes, out, numel, "qf_dequantize_block")) return rc;
+    if (map != 0 && map != 1) return fail(QF_ERR_BAD_ARG, "map must be 0 or 1");
+    if (numel == 0) return QF_OK;
+    if (!scales) return fail(QF_ERR_BAD_ARG, "scales is null");
+    QF_CUDA(cudaSetDevice(device));
+    const int vec = aligned(out, 16) && aligned(codes, 4);
+    qf::dequantize_block_kernel<<<flat_grid(numel), qf::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(codes, scales, numel,
+                                                                                                        map, out, vec);
+    QF_CUDA(cudaGetLastError());
+    return QF_OK;
+}
+
+int qf_quantize_rank1(const float* v, int64_t rows, int64_t cols, uint8_t* codes, float* row_max, float* col_max,
+                      int device, void* stream) {
+    g_err[0] = 0;
+    if (rows < 0 || cols < 0 || rows > INT32_MAX || cols > INT32_MAX) return fail(QF_ERR_BAD_ARG, "bad shape");
+    const int64_t numel = rows * cols;
+    if (numel == 0) return QF_OK;
+    if (!v || !codes || !row_max || !col_max) return fail(QF_ERR_BAD_ARG, "null pointer");
+    QF_CUDA(cudaSetDevice(device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    QF_CUDA(cudaMemsetAsync(row_max, 0, sizeof(float) * rows, st));
+    QF_CUDA(cudaMemsetAsync(col_max, 0, sizeof(float) * cols, st));
+    const int vec = aligned(v, 16) && aligned(codes, 4);
+    const int panel = vec && cols % qf::kPanelCols == 0;
+    const int64_t items = panel ? (rows + qf::kRowsPerItem - 1) / qf::kRowsPerItem * (cols / qf::kPanelCols) : flat_items(numel);
+    unsigned grid;
+    if (int rc = grid_for(items, &grid)) return rc;
+    qf::rank1_max_kernel<<<grid, qf::kThreads, 0, st>>>(v, static_cast<int>(rows), static_cast<int>(cols), row_max, col_max, panel);
+    qf::rank1_codec_kernel<true><<<flat_grid(numel), qf::kThreads, 0, st>>>(v, codes, row_max, col_max, static_cast<int>(rows),
+                                                                           static_cast<int>(cols), nullptr, vec);
+    QF_CUDA(cudaGetLastError());
+    return QF_OK;
+}
+
+int qf_dequantize_rank1(const uint8_t* codes, const float* row_max, const float* col_max, int64_t rows, int64_t cols,
+                        float* out, int device, void* stream) {
+    g_err[0] = 0;
+    if (rows < 0 || cols < 0 || rows > INT32_MAX || cols > INT32_MAX) return fail(QF_ERR_BAD_ARG, "bad shape");
+    const int64_t numel = rows * cols;
+    if (numel == 0) return QF_OK;
+    if (!codes || !row_max || !col_max || !out) return fail(QF_ERR_BAD_ARG, "null pointer");
+    QF_CUDA(cudaSetDevice(device));
+    const int vec = aligned(out, 16) && aligned(codes, 4);
+    qf::rank1_codec_kernel<false><<<flat_grid(numel), qf::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        nullptr, const_cast<uint8_t*>(codes), row_max, col_max, static_cast<int>(rows), static_cast<int>(cols), out, vec);
+    QF_CUDA(cudaGetLastError());
+    return QF_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,325 @@
+"""FourBitAdamW: AdamW with 4-bit optimizer states, one fused multi-tensor CUDA launch per step.
+
+Drop-in for the reference's optimizer classes ``AdamWFused_QuantFour`` (optim/fused_quantfour.py:25-313)
+and ``AdamW_QuantFour`` (optim/adamw_fourbit_triton.py:137-382): same constructor arguments, defaults
+and ValueError checks (fused_quantfour.py:28-58), same ``step(closure)`` contract (:131-138), same
+per-parameter state keys (:61-70, :110-128).  Where the reference loops over parameters in Python and
+launches one kernel plus one device synchronisation per tensor (:171-292), this class hands the whole
+ragged parameter list to ``qf_step_multi`` once per step and never synchronises.
+
+State of a parameter ``p`` (what ``state_dict()`` carries):
+  ``step``              0-dim float32 CPU tensor
+  ``exp_avg``           int8 [ceil(numel/2)] packed 4-bit codes   (float32, shaped like p, if not quantized)
+  ``exp_avg_sq``        int8 [ceil(numel/2)] packed 4-bit codes   (float32, shaped like p, if not quantized)
+  ``momentum_qstate``   {"enable": bool, "overhead": {"max1": float32 [ceil(numel/128)]}, "qmap": None}
+  ``variance_qstate``   {"enable": bool, "overhead": {...}, "qmap": None} where overhead is
+                        2-D p:  {"max_dims": [float32 [R,1], float32 [1,C]], "max1": None, "dim": 2}
+                        else:   {"max1": float32 [ceil(numel/128)], "dim": p.dim()}
+Quantization is enabled iff ``numel > quant_threshold`` (fused_quantfour.py:18-22; threshold 4096 as in
+adamw_fourbit_triton.py:118, :128).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from itertools import chain
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+
+from . import _lib
+from .functional import _DTYPES, dequantize_m, dequantize_v, dequantize_v_block
+
+__all__ = ["FourBitAdamW", "AdamWFused_QuantFour", "AdamW_Fused_QuantFour", "AdamW_QuantFour", "make_hyper",
+           "enable_param_quantization"]
+
+BLOCK = 128
+DEFAULT_THRESHOLD = 4096
+
+
+def enable_param_quantization(p, threshold) -> bool:
+    """Only tensors with more than ``threshold`` elements are quantized (fused_quantfour.py:18-22)."""
+    if threshold and p.numel() <= threshold:
+        return False
+    return True
+
+
+def make_hyper(lr: float, beta1: float, beta2: float, eps: float, weight_decay: float, step: float) -> _lib.QfHyper:
+    """Scalars of one step, derived in Python doubles like the reference's PyTorch path
+    (adamw_fourbit_triton.py:415, :458-465) and rounded once to float32 by ctypes."""
+    bc1 = 1 - beta1 ** step
+    bc2 = 1 - beta2 ** step
+    return _lib.QfHyper(1 - lr * weight_decay, 1 - beta1, beta2, 1 - beta2, eps, -(lr / bc1), math.sqrt(bc2), 0.0)
+
+
+def state_kind(p: torch.Tensor, threshold: int) -> int:
+    if not enable_param_quantization(p, threshold):
+        return _lib.QF_KIND_FP32
+    return _lib.QF_KIND_RANK1 if p.dim() == 2 else _lib.QF_KIND_BLOCK
+
+
+class _DevicePlan:
+    """Cached ctypes descriptor array + workspace for the tensors of one device."""
+
+    def __init__(self) -> None:
+        self.signature: Optional[tuple] = None
+        self.descs = None
+        self.workspace: Optional[torch.Tensor] = None
+        self.keepalive: list = []
+
+
+class FourBitAdamW(torch.optim.Optimizer):
+    """AdamW with decoupled weight decay whose moments are stored in 4 bits.
+
+    First moment: signed dynamic-exponent map, one abs-max scale per 128 elements.  Second moment:
+    unsigned linear map without zero; for 2-D parameters the scale of element (i, j) is
+    min(row_max[i], col_max[j]) (rank-1 normalisation), otherwise one scale per 128 elements.
+    Parameters with at most ``quant_threshold`` elements keep float32 moments.  Parameters and
+    gradients must be CUDA tensors of dtype float32 or bfloat16.
+    """
+
+    def __init__(
+        self,
+        params,
+        lr=1e-3,
+        betas=(0.9, 0.999),
+        eps=1e-8,
+        weight_decay=1e-2,
+        *,
+        fused: Optional[bool] = False,
+        quant_threshold: int = DEFAULT_THRESHOLD,
+    ):
+        if not 0.0 < lr:
+            raise ValueError(f"Invalid learning rate: {lr=}")
+        if not 0.0 < eps:
+            raise ValueError(f"Invalid eps value: {eps=}")
+        if not 0.0 < betas[0] < 1.0:
+            raise ValueError(f"Invalid Beta[0]: {betas[0]=}")
+        if not 0.0 < betas[1] < 1.0:
+            raise ValueError(f"Invalid Beta[1]: {betas[1]=}")
+        if not 0.0 <= weight_decay:
+            raise ValueError(f"Invalid weight_decay value: {weight_decay=}")
+        self.param_quant_threshold = int(quant_threshold)
+        defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, fused=fused)
+        super().__init__(params, defaults)
+        self._scratch: Dict[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]] = {}
+        self._plans: Dict[Tuple[int, int], _DevicePlan] = {}
+
+    # ---- state ---------------------------------------------------------------------------------
+
+    def init_qstate(self, p, state_name):
+        """Create the ``{state_name}_qstate`` record of ``p`` (fused_quantfour.py:61-70)."""
+        state = self.state[p]
+        state[f"{state_name}_qstate"] = {
+            "enable": enable_param_quantization(p, self.param_quant_threshold),
+            "overhead": dict(),
+            "qmap": None,
+        }
+
+    def _init_state(self, p: torch.Tensor) -> None:
+        state = self.state[p]
+        state["step"] = torch.tensor(0.0)
+        self.init_qstate(p, "momentum")
+        self.init_qstate(p, "variance")
+        n, dev = p.numel(), p.device
+        kind = state_kind(p, self.param_quant_threshold)
+        if kind == _lib.QF_KIND_FP32:
+            state["exp_avg"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.contiguous_format)
+            state["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.contiguous_format)
+            return
+        nb, nblk = (n + 1) // 2, (n + BLOCK - 1) // BLOCK
+        state["exp_avg"] = torch.zeros(nb, dtype=torch.int8, device=dev)
+        state["exp_avg_sq"] = torch.zeros(nb, dtype=torch.int8, device=dev)
+        state["momentum_qstate"]["overhead"]["max1"] = torch.zeros(nblk, dtype=torch.float32, device=dev)
+        vo = state["variance_qstate"]["overhead"]
+        vo["dim"] = p.dim()
+        if kind == _lib.QF_KIND_RANK1:
+            R, Cc = p.shape
+            vo["max_dims"] = [torch.zeros(R, 1, dtype=torch.float32, device=dev),
+                              torch.zeros(1, Cc, dtype=torch.float32, device=dev)]
+            vo["max1"] = None
+        else:
+            vo["max1"] = torch.zeros(nblk, dtype=torch.float32, device=dev)
+
+    def _scratch_for(self, p: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        s = self._scratch.get(p)
+        if s is None or s[0].device != p.device:
+            R, Cc = p.shape
+            s = (torch.zeros(R, dtype=torch.float32, device=p.device), torch.zeros(Cc, dtype=torch.float32, device=p.device))
+            self._scratch[p] = s
+        return s
+
+    def __setstate__(self, state: Dict[str, Any]) -> None:
+        super().__setstate__(state)
+        for group in self.param_groups:
+            group.setdefault("fused", None)
+        self.__dict__.setdefault("param_quant_threshold", DEFAULT_THRESHOLD)
+        self._scratch = {}
+        self._plans = {}
+        state_values = list(self.state.values())
+        step_is_tensor = len(state_values) != 0 and torch.is_tensor(state_values[0]["step"])
+        if not step_is_tensor:
+            for s in state_values:
+                s["step"] = torch.tensor(float(s["step"]))
+
+    def load_state_dict(self, state_dict: Dict[str, Any]) -> None:
+        """Load a state dict written by ``state_dict()``.
+
+        torch's loader casts every floating-point-parameter state tensor to the parameter's dtype,
+        which would turn int8 code buffers and float32 scales into bfloat16 for bf16 parameters.
+        After the base class has mapped ids and restored the groups, every state entry is therefore
+        re-materialised from the saved value with its saved dtype, on the parameter's device.
+        """
+        super().load_state_dict(state_dict)
+        saved_ids = chain.from_iterable(g["params"] for g in state_dict["param_groups"])
+        params = chain.from_iterable(g["params"] for g in self.param_groups)
+        id_map = dict(zip(saved_ids, params))
+
+        def place(value, device, key=None):
+            if torch.is_tensor(value):
+                return value.detach().clone() if key == "step" else value.detach().to(device=device, copy=True)
+            if isinstance(value, dict):
+                return {k: place(v, device, k) for k, v in value.items()}
+            if isinstance(value, (list, tuple)):
+                return type(value)(place(v, device) for v in value)
+            return value
+
+        for pid, saved in state_dict["state"].items():
+            if pid in id_map:
+                p = id_map[pid]
+                self.state[p] = place(saved, p.device)
+        self._scratch = {}
+        self._plans = {}
+
+    def dequantized_state(self, p: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """(exp_avg, exp_avg_sq) of ``p`` as float32 tensors shaped like ``p`` (dequantized on the GPU)."""
+        st = self.state[p]
+        if not st["momentum_qstate"]["enable"]:
+            return st["exp_avg"].clone(), st["exp_avg_sq"].clone()
+        n = p.numel()
+        m = dequantize_m(st["exp_avg"], st["momentum_qstate"]["overhead"]["max1"], n).view(p.shape)
+        vo = st["variance_qstate"]["overhead"]
+        if vo.get("max_dims") is not None:
+            row, col = vo["max_dims"]
+            v = dequantize_v(st["exp_avg_sq"], row.reshape(-1), col.reshape(-1))
+        else:
+            v = dequantize_v_block(st["exp_avg_sq"], vo["max1"], n).view(p.shape)
+        return m, v
+
+    # ---- step ----------------------------------------------------------------------------------
+
+    def _fill_desc(self, d: _lib.QfTensorDesc, p: torch.Tensor, g: torch.Tensor, st: Dict[str, Any], hyper: int) -> None:
+        n = p.numel()
+        d.p, d.g = p.data_ptr(), g.data_ptr()
+        d.m, d.v = st["exp_avg"].data_ptr(), st["exp_avg_sq"].data_ptr()
+        d.numel, d.dtype, d.hyper = n, _DTYPES[p.dtype], hyper
+        if not st["momentum_qstate"]["enable"]:
+            d.kind = _lib.QF_KIND_FP32
+            return
+        d.m_scale = st["momentum_qstate"]["overhead"]["max1"].data_ptr()
+        vo = st["variance_qstate"]["overhead"]
+        if vo.get("max_dims") is not None:
+            row, col = vo["max_dims"]
+            nrow, ncol = self._scratch_for(p)
+            d.kind = _lib.QF_KIND_RANK1
+            d.rows, d.cols = p.shape[0], p.shape[1]
+            d.v_scale, d.v_col = row.data_ptr(), col.data_ptr()
+            d.v_row_new, d.v_col_new = nrow.data_ptr(), ncol.data_ptr()
+        else:
+            d.kind = _lib.QF_KIND_BLOCK
+            d.v_scale = vo["max1"].data_ptr()
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        """Perform a single optimization step (fused_quantfour.py:131-138); returns the closure's loss."""
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+
+        hypers: List[_lib.QfHyper] = []
+        hyper_index: Dict[tuple, int] = {}
+        work: Dict[torch.device, List[tuple]] = {}
+        for group in self.param_groups:
+            beta1, beta2 = group["betas"]
+            gkey = (group["lr"], beta1, beta2, group["eps"], group["weight_decay"])
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                if p.grad.is_sparse:
+                    raise RuntimeError("QuantFour AdamW does not support sparse gradients")
+                if not p.is_cuda:
+                    raise RuntimeError("FourBitAdamW needs CUDA parameters; there is no CPU path")
+                if not p.is_contiguous():
+                    raise RuntimeError("param must be contiguous")
+                if p.dtype not in _DTYPES:
+                    raise TypeError(f"parameters must be float32 or bfloat16, got {p.dtype}")
+                g = p.grad
+                if g.dtype != p.dtype or g.numel() != p.numel() or g.device != p.device:
+                    raise RuntimeError("grad must match the parameter in dtype, numel and device")
+                if not g.is_contiguous():
+                    g = g.contiguous()
+                st = self.state[p]
+                if len(st) == 0:
+                    self._init_state(p)
+                st["step"] += 1
+                t = float(st["step"])
+                key = gkey + (t,)
+                hi = hyper_index.get(key)
+                if hi is None:
+                    hi = hyper_index[key] = len(hypers)
+                    hypers.append(make_hyper(*gkey, t))
+                work.setdefault(p.device, []).append((p, g, st, hi))
+
+        for dev, entries in work.items():
+            # a launch carries at most QF_MAX_HYPERS hyper-parameter sets: split by hyper index range
+            lo = 0
+            chunk = 0
+            while lo < len(hypers):
+                hi_end = lo + _lib.QF_MAX_HYPERS
+                sel = [e for e in entries if lo <= e[3] < hi_end]
+                if sel:
+                    self._launch(dev, chunk, sel, hypers[lo:hi_end], lo)
+                lo, chunk = hi_end, chunk + 1
+        return loss
+
+    def _launch(self, dev: torch.device, chunk: int, entries: List[tuple], hypers: List[_lib.QfHyper], hyper_base: int) -> None:
+        L = _lib.lib()
+        plan = self._plans.setdefault((dev.index, chunk), _DevicePlan())
+        signature = tuple((id(p), p.data_ptr(), g.data_ptr(), st["exp_avg"].data_ptr(), hi - hyper_base)
+                          for p, g, st, hi in entries)
+        if plan.signature != signature:
+            n = len(entries)
+            descs = (_lib.QfTensorDesc * n)()
+            for d, (p, g, st, hi) in zip(descs, entries):
+                self._fill_desc(d, p, g, st, hi - hyper_base)
+            need = L.qf_workspace_bytes(n)
+            if plan.workspace is None or plan.workspace.numel() < need or plan.workspace.device != dev:
+                plan.workspace = torch.zeros(need, dtype=torch.uint8, device=dev)
+            plan.descs, plan.signature = descs, signature
+            plan.keepalive = [g for _, g, _, _ in entries]
+        harr = (_lib.QfHyper * len(hypers))(*hypers)
+        rc = L.qf_step_multi(plan.descs, len(plan.descs), harr, len(hypers), plan.workspace.data_ptr(),
+                             plan.workspace.numel(), dev.index, C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+        _lib.check(rc, "qf_step_multi")
+
+    def nonfinite_seen(self) -> bool:
+        """Synchronise and report whether any step since the last call produced a non-finite scale."""
+        L = _lib.lib()
+        seen = False
+        for (dev_index, _), plan in self._plans.items():
+            if plan.workspace is None:
+                continue
+            word = C.c_uint32(0)
+            dev = torch.device("cuda", dev_index)
+            _lib.check(L.qf_read_status(plan.workspace.data_ptr(), dev_index,
+                                        C.c_void_p(torch.cuda.current_stream(dev).cuda_stream), C.byref(word)),
+                       "qf_read_status")
+            seen |= bool(word.value & _lib.QF_STATUS_NONFINITE)
+        return seen
+
+
+# The reference spells the class three ways (fused_quantfour.py:12, :25; adamw_fourbit_triton.py:137).
+AdamWFused_QuantFour = FourBitAdamW
+AdamW_Fused_QuantFour = FourBitAdamW
+AdamW_QuantFour = FourBitAdamW
