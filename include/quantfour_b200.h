@@ -80,8 +80,8 @@ typedef struct QfTensorDesc {
     float* m_scale;       /* [ceil(numel/128)]; unused for QF_KIND_FP32                          */
     float* v_scale;       /* BLOCK: [ceil(numel/128)]; RANK1: row maxima [rows]; in/out          */
     float* v_col;         /* RANK1: column maxima [cols]; in/out                                 */
-    float* v_row_new;     /* RANK1: scratch [rows] the step accumulates the new row maxima in    */
-    float* v_col_new;     /* RANK1: scratch [cols] for the new column maxima                     */
+    float* v_row_new;     /* RANK1: scratch [2*rows]: new row maxima, then their reciprocals     */
+    float* v_col_new;     /* RANK1: scratch [2*cols]: new column maxima, then their reciprocals  */
     int64_t numel;
     int64_t rows;         /* RANK1 only; rows * cols == numel                                    */
     int64_t cols;
@@ -108,8 +108,9 @@ size_t qf_workspace_bytes(int n_tensors);
  * cuda_adamw_kernels.cu:136-164, :422-469; driver loop optim/fused_quantfour.py:171-292).
  *
  * `descs` and `hypers` are host arrays.  For RANK1 tensors the call (1) clears v_row_new/v_col_new,
- * (2) accumulates the new maxima, (3) updates and requantizes using the old maxima for dequantize
- * and the new ones for quantize, (4) copies the new maxima into v_scale/v_col.
+ * (2) accumulates the new maxima, (3) stores their reciprocals in the second halves of the scratch
+ * arrays, updates and requantizes using the old maxima for dequantize and the new ones for quantize,
+ * (4) copies the new maxima into v_scale/v_col.
  */
 int qf_step_multi(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers,
                   void* workspace, size_t workspace_bytes, int device, void* stream);

@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libquantfour_b200.so")
+# QUANTFOUR_B200_LIB may name another build of the same library (e.g. one compiled with different tuning macros).
+LIB_PATH = os.environ.get("QUANTFOUR_B200_LIB") or os.path.join(HERE, "libquantfour_b200.so")
 
 QF_ABI_VERSION = 1
 QF_MAX_HYPERS = 16

@@ -32,7 +32,8 @@ int fail(int code, const char* fmt, ...) {
 
 constexpr size_t kStatusBytes = 256;  // head of the workspace: status word, then padding
 
-size_t table_bytes(int n) { return static_cast<size_t>(n) * sizeof(qf::DevTensor) + 2 * (static_cast<size_t>(n) + 1) * 8; }
+constexpr int kTables = 4;  // prefix sums: main/panel, main/flat, pre/panel, pre/flat
+size_t table_bytes(int n) { return static_cast<size_t>(n) * sizeof(qf::DevTensor) + kTables * (static_cast<size_t>(n) + 1) * 8; }
 size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
@@ -54,13 +55,13 @@ struct WsCache {
 std::mutex g_mu;
 std::unordered_map<uint64_t, WsCache> g_cache;
 
+enum { kMainPanel = 0, kMainFlat = 1, kPrePanel = 2, kPreFlat = 3 };
 struct Plan {
     int n = 0;                    // tensors in the table (zero-size tensors dropped)
-    int64_t main_items = 0, pre_items = 0;
+    int64_t items[kTables] = {0, 0, 0, 0};
     int n_rank1 = 0;
     qf::DevTensor* d_tensors = nullptr;
-    int64_t* d_main_base = nullptr;
-    int64_t* d_pre_base = nullptr;
+    int64_t* d_base[kTables] = {nullptr, nullptr, nullptr, nullptr};
     uint32_t* d_status = nullptr;
 };
 
@@ -76,7 +77,8 @@ int build_plan(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* wor
     if (!aligned(workspace, 256)) return fail(QF_ERR_BAD_ARG, "workspace must be 256-byte aligned");
 
     std::vector<qf::DevTensor> tab;
-    std::vector<int64_t> main_base{0}, pre_base{0};
+    std::vector<int64_t> base[kTables];
+    for (auto& b : base) b.push_back(0);
     tab.reserve(n_tensors);
     int n_rank1 = 0;
     for (int i = 0; i < n_tensors; ++i) {
@@ -129,32 +131,34 @@ int build_plan(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* wor
                 t.panels = static_cast<int32_t>(d.cols / qf::kPanelCols);
                 items = (d.rows + qf::kRowsPerItem - 1) / qf::kRowsPerItem * t.panels;
             }
-            pre_base.push_back(pre_base.back() + items);
             ++n_rank1;
-        } else {
-            pre_base.push_back(pre_base.back());
         }
         if (vec) t.flags |= qf::kFlagVec;
-        main_base.push_back(main_base.back() + items);
+        const bool panel = t.flags & qf::kFlagPanel, rank1 = d.kind == QF_KIND_RANK1;
+        base[kMainPanel].push_back(base[kMainPanel].back() + (panel ? items : 0));
+        base[kMainFlat].push_back(base[kMainFlat].back() + (panel ? 0 : items));
+        base[kPrePanel].push_back(base[kPrePanel].back() + (rank1 && panel ? items : 0));
+        base[kPreFlat].push_back(base[kPreFlat].back() + (rank1 && !panel ? items : 0));
         tab.push_back(t);
     }
     const int n = static_cast<int>(tab.size());
     plan->n = n;
     plan->n_rank1 = n_rank1;
-    plan->main_items = main_base.back();
-    plan->pre_items = pre_base.back();
     char* ws = static_cast<char*>(workspace);
     plan->d_status = reinterpret_cast<uint32_t*>(ws);
     plan->d_tensors = reinterpret_cast<qf::DevTensor*>(ws + kStatusBytes);
-    plan->d_main_base = reinterpret_cast<int64_t*>(ws + kStatusBytes + static_cast<size_t>(n) * sizeof(qf::DevTensor));
-    plan->d_pre_base = plan->d_main_base + (n + 1);
+    const size_t tensors_bytes = static_cast<size_t>(n) * sizeof(qf::DevTensor);
+    for (int k = 0; k < kTables; ++k) {
+        plan->items[k] = base[k].back();
+        plan->d_base[k] = reinterpret_cast<int64_t*>(ws + kStatusBytes + tensors_bytes) + static_cast<size_t>(k) * (n + 1);
+    }
     if (n == 0) return QF_OK;
 
     const size_t bytes = table_bytes(n);
     std::vector<char> host(bytes);
-    memcpy(host.data(), tab.data(), static_cast<size_t>(n) * sizeof(qf::DevTensor));
-    memcpy(host.data() + static_cast<size_t>(n) * sizeof(qf::DevTensor), main_base.data(), (n + 1) * 8);
-    memcpy(host.data() + static_cast<size_t>(n) * sizeof(qf::DevTensor) + (n + 1) * 8, pre_base.data(), (n + 1) * 8);
+    memcpy(host.data(), tab.data(), tensors_bytes);
+    for (int k = 0; k < kTables; ++k)
+        memcpy(host.data() + tensors_bytes + static_cast<size_t>(k) * (n + 1) * 8, base[k].data(), (n + 1) * 8);
 
     std::lock_guard<std::mutex> lock(g_mu);
     WsCache& c = g_cache[(static_cast<uint64_t>(device) << 56) ^ reinterpret_cast<uint64_t>(workspace)];
@@ -185,24 +189,61 @@ int grid_for(int64_t items, unsigned* grid) {
     return QF_OK;
 }
 
+void roll(const Plan& pl, int mode, cudaStream_t stream) {
+    qf::rank1_roll_kernel<<<pl.n * qf::kRollSlices, qf::kThreads, 0, stream>>>(pl.d_tensors, pl.n, mode);
+}
+
 int launch_pre(const Plan& pl, const qf::HyperPack& hp, cudaStream_t stream) {
     if (pl.n_rank1 == 0) return QF_OK;
-    qf::rank1_roll_kernel<<<pl.n * qf::kRollSlices, qf::kThreads, 0, stream>>>(pl.d_tensors, pl.n, 0);
+    roll(pl, qf::kRollClear, stream);
     unsigned grid;
-    if (int rc = grid_for(pl.pre_items, &grid)) return rc;
-    qf::step_pre_kernel<<<grid, qf::kThreads, 0, stream>>>(pl.d_tensors, pl.d_pre_base, pl.n, hp, pl.d_status);
+    if (pl.items[kPrePanel]) {
+        if (int rc = grid_for(pl.items[kPrePanel], &grid)) return rc;
+        qf::step_pre_kernel<true><<<grid, qf::kThreads, 0, stream>>>(pl.d_tensors, pl.d_base[kPrePanel], pl.n, hp, pl.d_status);
+    }
+    if (pl.items[kPreFlat]) {
+        if (int rc = grid_for(pl.items[kPreFlat], &grid)) return rc;
+        qf::step_pre_kernel<false><<<grid, qf::kThreads, 0, stream>>>(pl.d_tensors, pl.d_base[kPreFlat], pl.n, hp, pl.d_status);
+    }
     QF_CUDA(cudaGetLastError());
     return QF_OK;
 }
 
 int launch_main(const Plan& pl, const qf::HyperPack& hp, cudaStream_t stream) {
     if (pl.n == 0) return QF_OK;
+    if (pl.n_rank1) roll(pl, qf::kRollRecip, stream);
     unsigned grid;
-    if (int rc = grid_for(pl.main_items, &grid)) return rc;
-    qf::step_main_kernel<<<grid, qf::kThreads, 0, stream>>>(pl.d_tensors, pl.d_main_base, pl.n, hp, pl.d_status);
-    if (pl.n_rank1) qf::rank1_roll_kernel<<<pl.n * qf::kRollSlices, qf::kThreads, 0, stream>>>(pl.d_tensors, pl.n, 1);
+    if (pl.items[kMainPanel]) {
+        if (int rc = grid_for(pl.items[kMainPanel], &grid)) return rc;
+        QF_CUDA(cudaFuncSetAttribute(qf::step_main_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, qf::kMainDynSmem));
+        qf::step_main_kernel<true><<<grid, qf::kThreads, qf::kMainDynSmem, stream>>>(pl.d_tensors, pl.d_base[kMainPanel], pl.n, hp,
+                                                                                     pl.d_status);
+    }
+    if (pl.items[kMainFlat]) {
+        if (int rc = grid_for(pl.items[kMainFlat], &grid)) return rc;
+        qf::step_main_kernel<false><<<grid, qf::kThreads, 0, stream>>>(pl.d_tensors, pl.d_base[kMainFlat], pl.n, hp, pl.d_status);
+    }
+    if (pl.n_rank1) roll(pl, qf::kRollCommit, stream);
     QF_CUDA(cudaGetLastError());
     return QF_OK;
+}
+
+// The scalars as the kernels take them.  The packed sequences of the fast path need: finite scalars, an
+// eps that absorbs the square root of a denormal second moment (>= 2^-40), a bias correction whose
+// reciprocal is well defined, and a non-degenerate step size; anything else runs the exact path.
+qf::HyperDev widen_hyper(const QfHyper& h) {
+    qf::HyperDev d;
+    d.h = h;
+    d.rb = static_cast<float>(1.0 / static_cast<double>(h.bc2s));  // double rounding is harmless for 1/x
+    d.nb = -h.bc2s;
+    d.pad = 0;
+    const float all[] = {h.decay, h.w1, h.beta2, h.w2, h.eps, h.neg_step, h.bc2s};
+    bool ok = true;
+    for (float x : all) ok = ok && std::isfinite(x);
+    ok = ok && h.eps >= 0x1p-40f && h.eps <= 0x1p40f && h.bc2s >= 0x1p-30f && h.bc2s <= 2.0f;
+    ok = ok && std::fabs(h.neg_step) <= 0x1p40f && std::fabs(h.decay) <= 0x1p40f && h.beta2 >= 0.0f && h.w2 >= 0.0f;
+    d.fast = ok ? 1 : 0;
+    return d;
 }
 
 int step_common(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,
@@ -215,7 +256,7 @@ int step_common(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers,
     if (int rc = build_plan(descs, n_tensors, n_hypers, workspace, workspace_bytes, device, st, &pl)) return rc;
     qf::HyperPack hp;
     memset(&hp, 0, sizeof hp);
-    memcpy(hp.h, hypers, sizeof(QfHyper) * n_hypers);
+    for (int k = 0; k < n_hypers; ++k) hp.h[k] = widen_hyper(hypers[k]);
     if (pre)
         if (int rc = launch_pre(pl, hp, st)) return rc;
     if (main_)
@@ -309,7 +350,7 @@ int qf_fused_4bit(void* p, const void* g, void* exp, void* sq, float* exp_scale,
     QfHyper h;
     qf_make_hyper(lr, beta1, beta2, eps, weight_decay, step, &h);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    qf::single_tensor_kernel<<<flat_grid(numel), qf::kThreads, 0, st>>>(t, h);
+    qf::single_tensor_kernel<<<flat_grid(numel), qf::kThreads, 0, st>>>(t, widen_hyper(h));
     QF_CUDA(cudaGetLastError());
     return QF_OK;
 }
@@ -336,7 +377,7 @@ int qf_fused_single_tensor(void* p, const void* g, float* exp_avg, float* exp_av
     QfHyper h;
     qf_make_hyper(lr, beta1, beta2, eps, weight_decay, step, &h);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    qf::single_tensor_kernel<<<flat_grid(numel), qf::kThreads, 0, st>>>(t, h);
+    qf::single_tensor_kernel<<<flat_grid(numel), qf::kThreads, 0, st>>>(t, widen_hyper(h));
     QF_CUDA(cudaGetLastError());
     return QF_OK;
 }

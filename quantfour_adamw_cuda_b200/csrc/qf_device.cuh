@@ -139,6 +139,44 @@ struct Elem<__nv_bfloat16> {
     }
 };
 
+// Eight elements as loaded, not yet widened: lets a loop fetch the next row before it works on this one.
+template <typename T>
+struct Raw8;
+template <>
+struct Raw8<float> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const char* base, int64_t e) {
+        const float4* q = reinterpret_cast<const float4*>(base + e * 4);
+        a = q[0];
+        b = q[1];
+    }
+    // staged layout: two arrays of 32 16-byte vectors, lane-major (see main_panel)
+    __device__ __forceinline__ void from_shared(const char* arr, int lane) {
+        a = *reinterpret_cast<const float4*>(arr + lane * 16);
+        b = *reinterpret_cast<const float4*>(arr + (32 + lane) * 16);
+    }
+    __device__ __forceinline__ void widen(float (&x)[8]) const {
+        x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+        x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+    }
+};
+template <>
+struct Raw8<__nv_bfloat16> {
+    uint4 r;
+    __device__ __forceinline__ void from_shared(const char* arr, int lane) {
+        r = *reinterpret_cast<const uint4*>(arr + lane * 16);
+    }
+    __device__ __forceinline__ void load(const char* base, int64_t e) { r = *reinterpret_cast<const uint4*>(base + e * 2); }
+    __device__ __forceinline__ void widen(float (&x)[8]) const {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            x[2 * k] = __uint_as_float(w[k] << 16);
+            x[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+        }
+    }
+};
+
 __device__ __forceinline__ void load8f(const float* base, int64_t e, float (&x)[8]) {
     Elem<float>::load8(reinterpret_cast<const char*>(base), e, x);
 }

@@ -5,20 +5,30 @@
 // 128-element quantization blocks, and a block's abs-max is a 4-step shuffle among 16 lanes with no
 // shared memory and no CTA barrier.  A warp work item is
 //   * for rank-1 tensors whose column count is a multiple of 256 ("panel" mapping): kRowsPerItem rows
-//     of one 256-column panel.  A lane keeps the same 8 columns for the whole item, so the old and new
-//     column maxima live in registers and the first pass reduces column maxima over the rows in
-//     registers before touching global memory;
+//     of one 256-column panel.  A lane keeps the same 8 columns for the whole item, so everything that
+//     depends on the column only (old and new column maxima, their reciprocals) lives in registers, and
+//     the first pass reduces column maxima over the rows in registers before touching global memory;
 //   * otherwise ("flat" mapping): kRowsPerItem consecutive runs of 256 flattened elements.
-// A multi-tensor launch numbers the work items of all tensors consecutively; a warp finds its tensor
-// by binary search in the prefix-sum table.  CTAs hold 8 warps that take 8 consecutive items.
+// A multi-tensor launch numbers the work items of all tensors of one mapping consecutively; a warp finds
+// its tensor by binary search in the prefix-sum table.  CTAs hold 8 warps that take 8 consecutive items.
 //
-// Rank-1 second moments need the new row/column maxima of the whole tensor before any element can
-// be requantized, hence two passes: `pre` recomputes v from (g, old codes) and accumulates the
-// maxima with integer red.max on the bit patterns; `main` does the full update and recomputes the
-// identical v (same instruction sequence) to quantize it against the finished maxima.
+// Rank-1 second moments need the new row/column maxima of the whole tensor before any element can be
+// requantized, hence two passes: `pre` recomputes v from (g, old codes) and accumulates the maxima with
+// integer red.max on the bit patterns; `main` does the full update and recomputes the identical v to
+// quantize it against the finished maxima.  A small kernel in between stores the reciprocals of the new
+// maxima so that the main pass divides by multiplication plus exact residual correction.
+//
+// Arithmetic.  The path is instruction-issue bound on B200 if written with the general IEEE division and
+// square-root expansions (about 135 instructions per element), so the hot loops use the packed-fp32
+// sequences of qf_math.cuh (two elements per instruction, about 50 instructions per element) and take the
+// plain IEEE intrinsics of qf_device.cuh only where an operand leaves the range those sequences are valid
+// for.  Both give the same bits; the choice is warp-uniform.
 #pragma once
 
+#include <type_traits>
+
 #include "qf_device.cuh"
+#include "qf_math.cuh"
 
 namespace qf {
 
@@ -31,8 +41,8 @@ struct DevTensor {
     float* ms;
     float* vs;        // BLOCK: block scales; RANK1: row maxima
     float* vcol;
-    float* vrow_new;
-    float* vcol_new;
+    float* vrow_new;  // [2*rows]: new row maxima, then their reciprocals
+    float* vcol_new;  // [2*cols]: new column maxima, then their reciprocals
     int64_t numel;
     int32_t rows, cols;
     int32_t kind, dtype, hyper;
@@ -46,13 +56,107 @@ static_assert(sizeof(DevTensor) == 128, "DevTensor must stay 128 bytes");
 constexpr int kFlagVec = 1;    // every buffer is aligned for the vector path
 constexpr int kFlagPanel = 2;  // rank-1 tensor uses the panel mapping
 
+// Hyper-parameters as the kernels take them: the public scalars plus what the fast path needs.
+struct HyperDev {
+    QfHyper h;
+    float rb;    // RN(1 / bc2s)
+    float nb;    // -bc2s
+    int32_t fast;  // 0: the scalars are outside the ranges the fast sequences cover -> exact path only
+    int32_t pad;
+};
 struct HyperPack {
-    QfHyper h[QF_MAX_HYPERS];
+    HyperDev h[QF_MAX_HYPERS];
 };
 
-// Largest t with base[t] <= item, base[0] = 0, base[n] = total.
+// ---- first-moment search table ------------------------------------------------------------------------
+// Index = sign, exponent and two mantissa bits of x (bits 31..21).  The floats that share an index form an
+// interval that holds at most one of the 15 midpoints, so code(x) = base[index] + (thr[index] < x), with
+// thr = +inf where the interval holds none.  Built at compile time from the midpoints' bit patterns.
+struct LutEntry {
+    uint32_t thr;   // float bits
+    uint32_t base;
+};
+struct Lut {
+    LutEntry e[2048];
+};
+constexpr uint32_t kMidBits[15] = {0xbf466666u, 0xbf0ccccdu, 0xbea66666u, 0xbe147ae1u, 0xbd6147aeu,
+                                   0xbc9ba5e3u, 0xbb343958u, 0x3b343958u, 0x3c9ba5e3u, 0x3d6147aeu,
+                                   0x3e147ae1u, 0x3ea66666u, 0x3f0ccccdu, 0x3f466666u, 0x3f71999au};
+constexpr Lut make_lut() {
+    Lut t{};
+    for (int idx = 0; idx < 2048; ++idx) {
+        const uint32_t lo = static_cast<uint32_t>(idx & 1023) << 21, hi = lo | 0x1fffffu;  // magnitudes
+        uint32_t base = 0, thr = 0x7f800000u;
+        if (idx < 1024) {  // x >= 0: all seven negative midpoints are below
+            base = 7;
+            for (int k = 7; k < 15; ++k) {
+                if (kMidBits[k] < lo)
+                    ++base;
+                else if (kMidBits[k] <= hi)
+                    thr = kMidBits[k];
+            }
+        } else {  // x < 0: a midpoint -a is below the interval [-hi, -lo] iff a > hi
+            for (int k = 0; k < 7; ++k) {
+                const uint32_t a = kMidBits[k] & 0x7fffffffu;
+                if (a > hi)
+                    ++base;
+                else if (a >= lo)
+                    thr = kMidBits[k];
+            }
+        }
+        t.e[idx].thr = thr;
+        t.e[idx].base = base;
+    }
+    return t;
+}
+__device__ const Lut g_mlut = make_lut();
+
+// Shared memory of a CTA: the 16-entry tables (exact path), the first-moment search table, and two
+// byte-indexed pair tables for the fast dequantize: a byte of packed codes (two elements) fetches the two
+// map values of either moment with one 64-bit load.
+struct Smem {
+    Tables t;
+    LutEntry mlut[2048];
+    float2 qm2[256];   // (qm[b & 15], qm[b >> 4])
+    float2 qv2[256];   // (qv[b & 15], qv[b >> 4])
+};
+
+__device__ __forceinline__ void load_smem(Smem& s) {
+    for (int i = threadIdx.x; i < 2048; i += blockDim.x) s.mlut[i] = g_mlut.e[i];
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+        s.qm2[i] = make_float2(c_qm[i & 15], c_qm[i >> 4]);
+        s.qv2[i] = make_float2(c_qv[i & 15], c_qv[i >> 4]);
+    }
+    load_tables(s.t);  // ends with __syncthreads()
+}
+
+// Entry of a pair table for byte j (elements 2j, 2j+1) of a word of eight codes.
+__device__ __forceinline__ f2 pair_lookup(const float2* tab, uint32_t w, int j) {
+    const uint32_t off = j == 0 ? (w << 3) & 0x7f8u : (w >> (8 * j - 3)) & 0x7f8u;
+    return *reinterpret_cast<const float2*>(reinterpret_cast<const char*>(tab) + off);
+}
+
+__device__ __forceinline__ uint32_t search_m_lut(float x, const LutEntry* lut) {
+    const uint32_t b = __float_as_uint(x);
+    const LutEntry e = *reinterpret_cast<const LutEntry*>(reinterpret_cast<const char*>(lut) + ((b >> 18) & 0x3ff8u));
+    return e.base + (__uint_as_float(e.thr) < x ? 1u : 0u);
+}
+
+// Second-moment map: midpoints are (1.5 + k) / 16, so the count of midpoints below x is ceil(16 x - 1.5)
+// clamped to 0..15; 16 x - 1.5 is exact wherever it is positive.
+__device__ __forceinline__ uint32_t code_from_y(float y) {
+    uint32_t c;
+    asm("cvt.rpi.u32.f32 %0, %1;" : "=r"(c) : "f"(y));  // saturating: negative and NaN -> 0
+    return min(c, 15u);
+}
+__device__ __forceinline__ uint32_t search_v_closed(float x) { return code_from_y(__fmaf_rn(x, 16.0f, -1.5f)); }
+
+// A scale the fast division sequences may be used with.
+__device__ __forceinline__ bool scale_safe(float s) { return s == 0.0f || (s >= 0x1p-90f && s <= 0x1p100f); }
+
+// Largest t with base[t] <= item < base[t+1]; base[0] = 0, base[n] = total.
 __device__ __forceinline__ int find_tensor(const int64_t* __restrict__ base, int n, int64_t item) {
-    int lo = 0, hi = n;  // invariant: base[lo] <= item < base[hi]
+    int lo = 0, hi = n;
     while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
         if (__ldg(base + mid) <= item)
@@ -63,7 +167,7 @@ __device__ __forceinline__ int find_tensor(const int64_t* __restrict__ base, int
     return lo;
 }
 
-// ---- quantize helpers on a lane's 8 values -------------------------------------------------------
+// ---- exact-path helpers on a lane's 8 values ------------------------------------------------------------
 
 __device__ __forceinline__ uint32_t quantize8(const float (&x)[8], float scale, const float* mid, int nv) {
     uint32_t w = 0;
@@ -75,6 +179,7 @@ __device__ __forceinline__ uint32_t quantize8(const float (&x)[8], float scale, 
     return w;
 }
 
+// Max of |x| over the 16 lanes that hold one 128-element block.  Works on bit patterns, so a NaN survives.
 __device__ __forceinline__ float absmax8_bits_to_block(const float (&x)[8]) {
     uint32_t a = 0;
 #pragma unroll
@@ -86,12 +191,84 @@ __device__ __forceinline__ float absmax8_bits_to_block(const float (&x)[8]) {
     return __uint_as_float(a);
 }
 
+// ---- fast-path pieces -----------------------------------------------------------------------------------
+
+struct Hyper2 {  // the scalars of one step, broadcast into both halves of a packed register
+    f2 decay, w1, beta2, w2, eps, nstep, rb, nb;
+};
+__device__ __forceinline__ Hyper2 widen(const HyperDev& hd) {
+    Hyper2 o;
+    o.decay = bc2(hd.h.decay);
+    o.w1 = bc2(hd.h.w1);
+    o.beta2 = bc2(hd.h.beta2);
+    o.w2 = bc2(hd.h.w2);
+    o.eps = bc2(hd.h.eps);
+    o.nstep = bc2(hd.h.neg_step);
+    o.rb = bc2(hd.rb);
+    o.nb = bc2(hd.nb);
+    return o;
+}
+
+// The AdamW update of two elements; same roundings as adamw_elem.  V_FLOOR: the caller guarantees that the
+// old second moment is at least 2^-94 (a stored scale of at least 2^-90 times the smallest map value), so
+// the new one cannot fall below the range of the unchecked square root.
+template <bool V_FLOOR = false>
+__device__ __forceinline__ void adamw_pair(f2& p, f2 g, f2& m, f2& v, const Hyper2& h) {
+    // p * decay as a fused multiply-add with a zero addend: same value, but unlike a packed multiply it
+    // cannot be contracted with the add that consumes it further down (see qf_math.cuh).
+    const f2 p1 = fma2(p, h.decay, bc2(0.0f));
+    m = fma2(h.w1, fma2(m, bc2(-1.0f), g), m);            // m + w1 * (g - m)
+    v = fma2(mul2(h.w2, g), g, mul2(h.beta2, v));          // beta2 * v + (w2 * g) * g
+    const f2 s = sqrt2<!V_FLOOR>(v);
+    const f2 den = add2(div2_prepared(s, h.rb, h.nb), h.eps);
+    p = add2(p1, div2(mul2(h.nstep, m), den));
+}
+__device__ __forceinline__ f2 v_update2(f2 g, f2 v_old, const Hyper2& h) {
+    return fma2(mul2(h.w2, g), g, mul2(h.beta2, v_old));
+}
+
+// Code k of a word as the float 2^23 + code (mantissa trick); subtracting 2^23 - 1 gives code + 1 exactly.
+__device__ __forceinline__ float code_plus_2p23(uint32_t w, int k) {
+    return __uint_as_float(((w >> (4 * k)) & 15u) | 0x4b000000u);
+}
+constexpr float kMagic = -8388607.0f;
+
+// Exact quantization of four pairs, out of line: the rarely taken branch of the fast rows.
+__device__ __noinline__ uint32_t quantize8_pairs_exact(f2 a, f2 b, f2 c, f2 d, float scale, const float* mid) {
+    const float x[8] = {a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y};
+    return quantize8(x, scale, mid, 8);
+}
+
+// First-moment codes of a lane's 8 values against the block scale; fast division when the scale allows.
+__device__ __forceinline__ uint32_t quantize_m8(const f2 (&m)[4], float scale, const Smem& s) {
+    if (!scale_safe(scale)) return quantize8_pairs_exact(m[0], m[1], m[2], m[3], scale, s.t.mm);
+    const float r = scale == 0.0f ? 0.0f : __frcp_rn(scale);
+    const f2 r2 = bc2(r), ns2 = bc2(-scale);
+    uint32_t w = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const f2 q = div2_prepared(m[j], r2, ns2);
+        w += search_m_lut(q.x, s.mlut) << (8 * j);  // disjoint nibbles: add == or, and folds into a shift-add
+        w += search_m_lut(q.y, s.mlut) << (8 * j + 4);
+    }
+    return w;
+}
+
+// Max of |x| over the 128-element block a lane's 8 values belong to: 16 lanes, one redux instruction on
+// the bit patterns (non-negative floats order like unsigned integers); each half-warp names its own lanes.
+__device__ __forceinline__ float absmax_pairs_to_block(const f2 (&m)[4]) {
+    float a = fmaxf(fmaxf(fabsf(m[0].x), fabsf(m[0].y)), fmaxf(fabsf(m[1].x), fabsf(m[1].y)));
+    a = fmaxf(a, fmaxf(fmaxf(fabsf(m[2].x), fabsf(m[2].y)), fmaxf(fabsf(m[3].x), fabsf(m[3].y))));
+    const unsigned mask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
+    return __uint_as_float(__reduce_max_sync(mask, __float_as_uint(a)));
+}
+
 // =================================================================================================
 // Panel mapping, rank-1 tensors
 // =================================================================================================
 
 template <typename T>
-__device__ __forceinline__ void pre_panel(const DevTensor& t, int64_t li, const QfHyper& h, const Tables& s,
+__device__ __forceinline__ void pre_panel(const DevTensor& t, int64_t li, const HyperDev& hd, const Smem& s,
                                           uint32_t* status) {
     const int lane = threadIdx.x & 31;
     const int band = static_cast<int>(li / t.panels);
@@ -101,76 +278,238 @@ __device__ __forceinline__ void pre_panel(const DevTensor& t, int64_t li, const 
     const int j0 = panel * kPanelCols + lane * 8;
     float col_old[8];
     load8f(t.vcol, j0, col_old);
+    const Hyper2 h2 = widen(hd);
     uint32_t cmax[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) cmax[k] = 0;
     const uint8_t* vc = reinterpret_cast<const uint8_t*>(t.v);
-    for (int r = r0; r < r1; ++r) {
-        const int64_t e = static_cast<int64_t>(r) * t.cols + j0;
-        float g[8];
-        Elem<T>::load8(t.g, e, g);
-        const uint32_t wv = *reinterpret_cast<const uint32_t*>(vc + (e >> 1));
-        const float row_old = __ldg(t.vs + r);
-        uint32_t rmax = 0;
+    // Four rows per trip, all their loads issued before the first is worked on: this pass does little
+    // arithmetic per byte, so it needs many bytes in flight per warp to cover HBM latency.
+    constexpr int kBatch = 4;
+    for (int rb = r0; rb < r1; rb += kBatch) {
+        Raw8<T> g_raw[kBatch];
+        uint32_t wvs[kBatch];
+        float rows_old[kBatch];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const float v_old = __fmul_rn(s.qv[nib(wv, k)], fminf(row_old, col_old[k]));
-            const uint32_t b = __float_as_uint(v_update(g[k], v_old, h));  // v >= 0: bits order like values
-            rmax = max(rmax, b);
-            cmax[k] = max(cmax[k], b);
+        for (int i = 0; i < kBatch; ++i) {
+            const int r = min(rb + i, r1 - 1);  // past the end: reload the last row (its maxima do not change)
+            const int64_t e = static_cast<int64_t>(r) * t.cols + j0;
+            g_raw[i].load(t.g, e);
+            wvs[i] = *reinterpret_cast<const uint32_t*>(vc + (e >> 1));
+            rows_old[i] = __ldg(t.vs + r);
         }
-        rmax = __reduce_max_sync(kFull, rmax);
-        if (lane == 0) {
-            atomic_max_nonneg(t.vrow_new + r, rmax);
-            if (rmax >= 0x7f800000u) atomicOr(status, QF_STATUS_NONFINITE);
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i) {
+            const int r = min(rb + i, r1 - 1);
+            const uint32_t wv = wvs[i];
+            const float row_old = rows_old[i];
+            float g[8];
+            g_raw[i].widen(g);
+            uint32_t rmax = 0;
+            if (hd.fast) {  // warp-uniform
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const f2 v_old = mul2(pair_lookup(s.qv2, wv, j),
+                                          mk2(fminf(row_old, col_old[2 * j]), fminf(row_old, col_old[2 * j + 1])));
+                    const f2 v = v_update2(mk2(g[2 * j], g[2 * j + 1]), v_old, h2);
+                    const uint32_t b0 = __float_as_uint(v.x), b1 = __float_as_uint(v.y);  // v >= 0
+                    rmax = max(rmax, max(b0, b1));
+                    cmax[2 * j] = max(cmax[2 * j], b0);
+                    cmax[2 * j + 1] = max(cmax[2 * j + 1], b1);
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const float v_old = __fmul_rn(s.t.qv[nib(wv, k)], fminf(row_old, col_old[k]));
+                    const uint32_t b = __float_as_uint(v_update(g[k], v_old, hd.h));
+                    rmax = max(rmax, b);
+                    cmax[k] = max(cmax[k], b);
+                }
+            }
+            rmax = __reduce_max_sync(kFull, rmax);
+            if (lane == 0) {
+                atomic_max_nonneg(t.vrow_new + r, rmax);
+                if (rmax >= 0x7f800000u) atomicOr(status, QF_STATUS_NONFINITE);
+            }
         }
     }
 #pragma unroll
     for (int k = 0; k < 8; ++k) atomic_max_nonneg(t.vcol_new + j0 + k, cmax[k]);
 }
 
+// One row of a panel, exact arithmetic (also the reference for what the fast row must produce).  Kept out
+// of line and self-contained (it reloads its column maxima) so that it costs the hot loop no registers.
 template <typename T>
-__device__ __forceinline__ void main_panel(const DevTensor& t, int64_t li, const QfHyper& h, const Tables& s,
-                                           uint32_t* status) {
+__device__ __noinline__ void main_panel_row_exact(const DevTensor* tp, int64_t e, int r, int j0, const HyperDev& hd,
+                                                  const Smem& s, uint32_t* status) {
+    const DevTensor t = *tp;
+    const int lane = threadIdx.x & 31;
+    uint8_t* mc = reinterpret_cast<uint8_t*>(t.m);
+    uint8_t* vc = reinterpret_cast<uint8_t*>(t.v);
+    float p[8], g[8], m[8], v[8], col_old[8], col_new[8];
+    load8f(t.vcol, j0, col_old);
+    load8f(t.vcol_new, j0, col_new);
+    Elem<T>::load8(t.p, e, p);
+    Elem<T>::load8(t.g, e, g);
+    const uint32_t wm = *reinterpret_cast<const uint32_t*>(mc + (e >> 1));
+    const uint32_t wv = *reinterpret_cast<const uint32_t*>(vc + (e >> 1));
+    const float ms_old = __ldg(t.ms + (e >> 7));
+    const float row_old = __ldg(t.vs + r);
+    const float row_new = t.vrow_new[r];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        m[k] = __fmul_rn(s.t.qm[nib(wm, k)], ms_old);
+        v[k] = __fmul_rn(s.t.qv[nib(wv, k)], fminf(row_old, col_old[k]));
+        adamw_elem(p[k], g[k], m[k], v[k], hd.h);
+    }
+    Elem<T>::store8(t.p, e, p);
+    const float ms_new = absmax8_bits_to_block(m);
+    *reinterpret_cast<uint32_t*>(mc + (e >> 1)) = quantize8(m, ms_new, s.t.mm, 8);
+    if ((lane & 15) == 0) {
+        t.ms[e >> 7] = ms_new;
+        if (nonfinite(ms_new)) atomicOr(status, QF_STATUS_NONFINITE);
+    }
+    uint32_t w = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) w |= search16(scaled(v[k], fminf(row_new, col_new[k])), s.t.mv) << (4 * k);
+    *reinterpret_cast<uint32_t*>(vc + (e >> 1)) = w;
+}
+
+// ---- asynchronous staging of the rows of a panel ---------------------------------------------------------
+// Each lane copies its own 16-byte pieces of p and g and its two code words of the rows ahead into a
+// per-warp ring in shared memory with cp.async and reads them back when their row comes up.  A lane only
+// ever reads what it copied itself, so the ring needs no barrier: cp.async.wait_group orders a lane's
+// copies with its own reads.  kStages - 1 rows are in flight per warp, which holds enough bytes in flight
+// per SM to cover HBM latency at two CTAs per SM without spending registers on it.
+constexpr int kStages = 4;
+constexpr int kStageRowBytesMax = 32 * (2 * 2 * 16 + 8);            // fp32 parameters: 2304 bytes per row
+constexpr int kMainDynSmem = kWarpsPerCta * kStages * kStageRowBytesMax;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<unsigned>(__cvta_generic_to_shared(smem))),
+                 "l"(__cvta_generic_to_global(gmem))
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<unsigned>(__cvta_generic_to_shared(smem))),
+                 "l"(__cvta_generic_to_global(gmem))
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <typename T>
+__device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, const HyperDev& hd, const Smem& s,
+                                           char* stage, uint32_t* status) {
+    const DevTensor t = *tp;
     const int lane = threadIdx.x & 31;
     const int band = static_cast<int>(li / t.panels);
     const int panel = static_cast<int>(li - static_cast<int64_t>(band) * t.panels);
     const int r0 = band * kRowsPerItem;
     const int r1 = min(r0 + kRowsPerItem, t.rows);
     const int j0 = panel * kPanelCols + lane * 8;
-    float col_old[8], col_new[8];
-    load8f(t.vcol, j0, col_old);
-    load8f(t.vcol_new, j0, col_new);
     uint8_t* mc = reinterpret_cast<uint8_t*>(t.m);
     uint8_t* vc = reinterpret_cast<uint8_t*>(t.v);
-    for (int r = r0; r < r1; ++r) {
-        const int64_t e = static_cast<int64_t>(r) * t.cols + j0;
-        float p[8], g[8], m[8], v[8];
-        Elem<T>::load8(t.p, e, p);
-        Elem<T>::load8(t.g, e, g);
-        const uint32_t wm = *reinterpret_cast<const uint32_t*>(mc + (e >> 1));
-        const uint32_t wv = *reinterpret_cast<const uint32_t*>(vc + (e >> 1));
-        const float ms_old = __ldg(t.ms + (e >> 7));
-        const float row_old = __ldg(t.vs + r);
-        const float row_new = t.vrow_new[r];
+
+    constexpr int NV = sizeof(T) / 2;  // 16-byte vectors per lane and array: 1 (bf16) or 2 (fp32)
+    constexpr int kArr = NV * 512;     // bytes of one staged array of one row
+    constexpr int kRowBytes = 2 * kArr + 256;
+    auto issue = [&](int r, int slot) {
+        if (r < r1) {
+            const int64_t e = static_cast<int64_t>(r) * t.cols + j0;
+            char* base = stage + slot * kRowBytes;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            m[k] = __fmul_rn(s.qm[nib(wm, k)], ms_old);
-            v[k] = __fmul_rn(s.qv[nib(wv, k)], fminf(row_old, col_old[k]));
-            adamw_elem(p[k], g[k], m[k], v[k], h);
+            for (int v = 0; v < NV; ++v) {
+                cp_async16(base + (v * 32 + lane) * 16, t.p + e * sizeof(T) + v * 16);
+                cp_async16(base + kArr + (v * 32 + lane) * 16, t.g + e * sizeof(T) + v * 16);
+            }
+            cp_async4(base + 2 * kArr + lane * 4, mc + (e >> 1));
+            cp_async4(base + 2 * kArr + 128 + lane * 4, vc + (e >> 1));
+        }
+        cp_async_commit();  // one group per row, empty past the end, so that the group count stays in step
+    };
+#pragma unroll
+    for (int i = 0; i < kStages - 1; ++i) issue(r0 + i, i);
+
+    float col_old[8], col_new[8], rcol[8];
+    load8f(t.vcol, j0, col_old);
+    load8f(t.vcol_new, j0, col_new);
+    load8f(t.vcol_new + t.cols, j0, rcol);
+    // The pass that stored the reciprocals wrote NaN where an old or new maximum is outside the range of
+    // the fast sequences.  A zero old maximum (first step, rows never touched) lets v fall below the range
+    // of the unchecked square root, so such rows and columns take the exact path as well.
+    bool ok = hd.fast;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ok &= rcol[k] == rcol[k] && col_old[k] > 0.0f;
+    const bool col_fast = __all_sync(kFull, ok);
+    const Hyper2 h2 = widen(hd);
+
+    struct RowScalars {
+        float ms_old, row_old, row_new, rrow;
+    };
+    auto fetch_scalars = [&](int r) {
+        RowScalars o;
+        const int64_t e = static_cast<int64_t>(r) * t.cols + j0;
+        o.ms_old = __ldg(t.ms + (e >> 7));
+        o.row_old = __ldg(t.vs + r);
+        o.row_new = __ldcg(t.vrow_new + r);
+        o.rrow = __ldcg(t.vrow_new + t.rows + r);
+        return o;
+    };
+    RowScalars sc_next = fetch_scalars(r0);
+    int slot = 0;
+    for (int r = r0; r < r1; ++r) {
+        issue(r + kStages - 1, slot == 0 ? kStages - 1 : slot - 1);  // refill the slot the previous row used
+        const RowScalars sc = sc_next;
+        if (r + 1 < r1) sc_next = fetch_scalars(r + 1);
+        cp_async_wait<kStages - 1>();  // everything but the newest kStages-1 groups has landed: row r is there
+        const char* base = stage + slot * kRowBytes;
+        slot = slot + 1 == kStages ? 0 : slot + 1;
+        const int64_t e = static_cast<int64_t>(r) * t.cols + j0;
+        if (!(col_fast && sc.rrow == sc.rrow && sc.row_old > 0.0f)) {  // warp-uniform
+            main_panel_row_exact<T>(tp, e, r, j0, hd, s, status);
+            continue;
+        }
+        Raw8<T> praw, graw;
+        praw.from_shared(base, lane);
+        graw.from_shared(base + kArr, lane);
+        const uint32_t wm = *reinterpret_cast<const uint32_t*>(base + 2 * kArr + lane * 4);
+        const uint32_t wv = *reinterpret_cast<const uint32_t*>(base + 2 * kArr + 128 + lane * 4);
+        float p[8], g[8];
+        praw.widen(p);
+        graw.widen(g);
+        const f2 ms_old = bc2(sc.ms_old);
+        const float row_old = sc.row_old, row_new = sc.row_new, rrow = sc.rrow;
+        f2 m[4];
+        uint32_t wq = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            f2 pp = mk2(p[2 * j], p[2 * j + 1]);
+            m[j] = mul2(pair_lookup(s.qm2, wm, j), ms_old);
+            f2 v = mul2(pair_lookup(s.qv2, wv, j), mk2(fminf(row_old, col_old[2 * j]), fminf(row_old, col_old[2 * j + 1])));
+            adamw_pair<true>(pp, mk2(g[2 * j], g[2 * j + 1]), m[j], v, h2);
+            p[2 * j] = pp.x;
+            p[2 * j + 1] = pp.y;
+            // requantize v: scale = min(row', col') -> -scale = max(-row', -col'), 1/scale = max(1/row', 1/col')
+            const f2 nsv = mk2(fmaxf(-row_new, -col_new[2 * j]), fmaxf(-row_new, -col_new[2 * j + 1]));
+            const f2 rv = mk2(fmaxf(rrow, rcol[2 * j]), fmaxf(rrow, rcol[2 * j + 1]));
+            const f2 y = fma2(div2_prepared(v, rv, nsv), bc2(16.0f), bc2(-1.5f));
+            wq += code_from_y(y.x) << (8 * j);
+            wq += code_from_y(y.y) << (8 * j + 4);
         }
         Elem<T>::store8(t.p, e, p);
-        const float ms_new = absmax8_bits_to_block(m);
-        *reinterpret_cast<uint32_t*>(mc + (e >> 1)) = quantize8(m, ms_new, s.mm, 8);
+        *reinterpret_cast<uint32_t*>(vc + (e >> 1)) = wq;
+        const float ms_new = absmax_pairs_to_block(m);
+        *reinterpret_cast<uint32_t*>(mc + (e >> 1)) = quantize_m8(m, ms_new, s);
         if ((lane & 15) == 0) {
             t.ms[e >> 7] = ms_new;
             if (nonfinite(ms_new)) atomicOr(status, QF_STATUS_NONFINITE);
         }
-        uint32_t w = 0;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) w |= search16(scaled(v[k], fminf(row_new, col_new[k])), s.mv) << (4 * k);
-        *reinterpret_cast<uint32_t*>(vc + (e >> 1)) = w;
     }
+    cp_async_wait<0>();
 }
 
 // =================================================================================================
@@ -224,7 +563,7 @@ __device__ __forceinline__ void rank1_scales(const float* row, const float* col,
 }
 
 template <typename T>
-__device__ __forceinline__ void pre_flat_rank1(const DevTensor& t, int64_t li, const QfHyper& h, const Tables& s,
+__device__ __forceinline__ void pre_flat_rank1(const DevTensor& t, int64_t li, const HyperDev& hd, const Smem& s,
                                                uint32_t* status) {
     const int lane = threadIdx.x & 31;
     const bool vec = t.flags & kFlagVec;
@@ -244,7 +583,7 @@ __device__ __forceinline__ void pre_flat_rank1(const DevTensor& t, int64_t li, c
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             if (k < nv) {
-                const uint32_t b = __float_as_uint(v_update(g[k], __fmul_rn(s.qv[nib(wv, k)], sc[k]), h));
+                const uint32_t b = __float_as_uint(v_update(g[k], __fmul_rn(s.t.qv[nib(wv, k)], sc[k]), hd.h));
                 atomic_max_nonneg(t.vrow_new + ri[k], b);
                 atomic_max_nonneg(t.vcol_new + ci[k], b);
                 if (b >= 0x7f800000u) atomicOr(status, QF_STATUS_NONFINITE);
@@ -253,95 +592,180 @@ __device__ __forceinline__ void pre_flat_rank1(const DevTensor& t, int64_t li, c
     }
 }
 
+// One run of 256 flattened elements, exact arithmetic, any tail, any alignment.
 template <typename T, int KIND>
-__device__ __forceinline__ void main_flat(const DevTensor& t, int64_t li, const QfHyper& h, const Tables& s,
-                                          uint32_t* status) {
+__device__ __noinline__ void main_flat_run_exact(const DevTensor* tp, int64_t wbase, const HyperDev& hd, const Smem& s,
+                                                 uint32_t* status) {
+    const DevTensor t = *tp;
     const int lane = threadIdx.x & 31;
     const bool vec = t.flags & kFlagVec;
-    const int64_t start = li * (kPanelCols * kRowsPerItem);
     uint8_t* mc = reinterpret_cast<uint8_t*>(t.m);
     uint8_t* vc = reinterpret_cast<uint8_t*>(t.v);
+    const int64_t e = wbase + lane * 8;
+    const int nv = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(8), t.numel - e)));
+    float p[8], g[8], m[8], v[8];
+    load8_masked<T>(t.p, e, nv, vec, p);
+    load8_masked<T>(t.g, e, nv, vec, g);
+    if (KIND == QF_KIND_FP32) {
+        load8_masked<float>(t.m, e, nv, vec, m);
+        load8_masked<float>(t.v, e, nv, vec, v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) adamw_elem(p[k], g[k], m[k], v[k], hd.h);
+        store8_masked<T>(t.p, e, nv, vec, p);
+        store8_masked<float>(t.m, e, nv, vec, m);
+        store8_masked<float>(t.v, e, nv, vec, v);
+        return;
+    }
+    const uint32_t wm = nv ? load_codes(mc, e, nv, vec) : 0u;
+    const uint32_t wv = nv ? load_codes(vc, e, nv, vec) : 0u;
+    const float ms_old = nv ? __ldg(t.ms + (e >> 7)) : 0.0f;
+    float sc_old[8], sc_new[8];
+    if (KIND == QF_KIND_BLOCK) {
+        const float vs_old = nv ? __ldg(t.vs + (e >> 7)) : 0.0f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) sc_old[k] = vs_old;
+    } else {
+        int ri[8], ci[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) sc_old[k] = sc_new[k] = 0.0f;
+        if (nv) {
+            rank1_scales(t.vs, t.vcol, e, nv, t.cols, sc_old, ri, ci);
+            rank1_scales(t.vrow_new, t.vcol_new, e, nv, t.cols, sc_new, ri, ci);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        m[k] = __fmul_rn(s.t.qm[nib(wm, k)], ms_old);
+        v[k] = __fmul_rn(s.t.qv[nib(wv, k)], sc_old[k]);
+        adamw_elem(p[k], g[k], m[k], v[k], hd.h);
+        if (k >= nv) {  // padding of the last block counts as zero
+            m[k] = 0.0f;
+            v[k] = 0.0f;
+        }
+    }
+    store8_masked<T>(t.p, e, nv, vec, p);
+    const float ms_new = absmax8_bits_to_block(m);  // all 32 lanes take part in the shuffles
+    float vs_new = 0.0f;
+    if (KIND == QF_KIND_BLOCK) vs_new = absmax8_bits_to_block(v);
+    if (nv == 0) return;
+    store_codes(mc, e, nv, vec, quantize8(m, ms_new, s.t.mm, nv));
+    uint32_t w = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float sv = KIND == QF_KIND_BLOCK ? vs_new : sc_new[k];
+        const uint32_t c = search16(scaled(v[k], sv), s.t.mv);
+        w |= (k < nv ? c : 0u) << (4 * k);
+    }
+    store_codes(vc, e, nv, vec, w);
+    if ((lane & 15) == 0) {
+        t.ms[e >> 7] = ms_new;
+        if (KIND == QF_KIND_BLOCK) t.vs[e >> 7] = vs_new;
+        if (nonfinite(ms_new) || nonfinite(vs_new)) atomicOr(status, QF_STATUS_NONFINITE);
+    }
+}
+
+// One full, vector-aligned run of 256 elements with the packed arithmetic (block-128 and fp32-state kinds).
+template <typename T, int KIND>
+__device__ __forceinline__ void main_flat_run_fast(const DevTensor& t, int64_t wbase, const Hyper2& h2, const Smem& s,
+                                                   uint32_t* status) {
+    const int lane = threadIdx.x & 31;
+    const int64_t e = wbase + lane * 8;
+    float p[8], g[8];
+    Elem<T>::load8(t.p, e, p);
+    Elem<T>::load8(t.g, e, g);
+    if (KIND == QF_KIND_FP32) {
+        float m[8], v[8];
+        Elem<float>::load8(t.m, e, m);
+        Elem<float>::load8(t.v, e, v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            f2 pp = mk2(p[2 * j], p[2 * j + 1]), mm = mk2(m[2 * j], m[2 * j + 1]), vv = mk2(v[2 * j], v[2 * j + 1]);
+            adamw_pair(pp, mk2(g[2 * j], g[2 * j + 1]), mm, vv, h2);
+            p[2 * j] = pp.x; p[2 * j + 1] = pp.y;
+            m[2 * j] = mm.x; m[2 * j + 1] = mm.y;
+            v[2 * j] = vv.x; v[2 * j + 1] = vv.y;
+        }
+        Elem<T>::store8(t.p, e, p);
+        Elem<float>::store8(t.m, e, m);
+        Elem<float>::store8(t.v, e, v);
+        return;
+    }
+    uint8_t* mc = reinterpret_cast<uint8_t*>(t.m);
+    uint8_t* vc = reinterpret_cast<uint8_t*>(t.v);
+    const uint32_t wm = *reinterpret_cast<const uint32_t*>(mc + (e >> 1));
+    const uint32_t wv = *reinterpret_cast<const uint32_t*>(vc + (e >> 1));
+    const f2 ms_old = bc2(__ldg(t.ms + (e >> 7)));
+    const float vs_old = __ldg(t.vs + (e >> 7));
+    const f2 vs2 = bc2(vs_old);
+    f2 m[4], v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        f2 pp = mk2(p[2 * j], p[2 * j + 1]);
+        m[j] = mul2(pair_lookup(s.qm2, wm, j), ms_old);
+        v[j] = mul2(pair_lookup(s.qv2, wv, j), vs2);
+        adamw_pair(pp, mk2(g[2 * j], g[2 * j + 1]), m[j], v[j], h2);
+        p[2 * j] = pp.x;
+        p[2 * j + 1] = pp.y;
+    }
+    Elem<T>::store8(t.p, e, p);
+    const float ms_new = absmax_pairs_to_block(m);
+    const float vs_new = absmax_pairs_to_block(v);
+    *reinterpret_cast<uint32_t*>(mc + (e >> 1)) = quantize_m8(m, ms_new, s);
+    uint32_t wq = 0;
+    if (scale_safe(vs_new)) {
+        const f2 r2 = bc2(vs_new == 0.0f ? 0.0f : __frcp_rn(vs_new)), ns2 = bc2(-vs_new);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const f2 y = fma2(div2_prepared(v[j], r2, ns2), bc2(16.0f), bc2(-1.5f));
+            wq += code_from_y(y.x) << (8 * j);
+            wq += code_from_y(y.y) << (8 * j + 4);
+        }
+    } else {
+        wq = quantize8_pairs_exact(v[0], v[1], v[2], v[3], vs_new, s.t.mv);
+    }
+    *reinterpret_cast<uint32_t*>(vc + (e >> 1)) = wq;
+    if ((lane & 15) == 0) {
+        t.ms[e >> 7] = ms_new;
+        t.vs[e >> 7] = vs_new;
+        if (nonfinite(ms_new) || nonfinite(vs_new)) atomicOr(status, QF_STATUS_NONFINITE);
+    }
+}
+
+template <typename T, int KIND>
+__device__ __forceinline__ void main_flat(const DevTensor* tp, int64_t li, const HyperDev& hd, const Smem& s,
+                                          uint32_t* status) {
+    const DevTensor t = *tp;
+    const bool vec = t.flags & kFlagVec;
+    const int64_t start = li * (kPanelCols * kRowsPerItem);
+    const Hyper2 h2 = widen(hd);
     for (int it = 0; it < kRowsPerItem; ++it) {
         const int64_t wbase = start + static_cast<int64_t>(it) * kPanelCols;
         if (wbase >= t.numel) break;  // warp-uniform
-        const int64_t e = wbase + lane * 8;
-        const int nv = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(8), t.numel - e)));
-        float p[8], g[8], m[8], v[8];
-        load8_masked<T>(t.p, e, nv, vec, p);
-        load8_masked<T>(t.g, e, nv, vec, g);
-        if (KIND == QF_KIND_FP32) {
-            load8_masked<float>(t.m, e, nv, vec, m);
-            load8_masked<float>(t.v, e, nv, vec, v);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) adamw_elem(p[k], g[k], m[k], v[k], h);
-            store8_masked<T>(t.p, e, nv, vec, p);
-            store8_masked<float>(t.m, e, nv, vec, m);
-            store8_masked<float>(t.v, e, nv, vec, v);
-            continue;
-        }
-        const uint32_t wm = nv ? load_codes(mc, e, nv, vec) : 0u;
-        const uint32_t wv = nv ? load_codes(vc, e, nv, vec) : 0u;
-        const float ms_old = nv ? __ldg(t.ms + (e >> 7)) : 0.0f;
-        float sc_old[8], sc_new[8];
-        if (KIND == QF_KIND_BLOCK) {
-            const float vs_old = nv ? __ldg(t.vs + (e >> 7)) : 0.0f;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) sc_old[k] = vs_old;
-        } else {
-            int ri[8], ci[8];
-            if (nv) {
-                rank1_scales(t.vs, t.vcol, e, nv, t.cols, sc_old, ri, ci);
-                rank1_scales(t.vrow_new, t.vcol_new, e, nv, t.cols, sc_new, ri, ci);
-            }
-        }
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            m[k] = __fmul_rn(s.qm[nib(wm, k)], ms_old);
-            v[k] = __fmul_rn(s.qv[nib(wv, k)], sc_old[k]);
-            adamw_elem(p[k], g[k], m[k], v[k], h);
-            if (k >= nv) {  // padding of the last block counts as zero
-                m[k] = 0.0f;
-                v[k] = 0.0f;
-            }
-        }
-        store8_masked<T>(t.p, e, nv, vec, p);
-        const float ms_new = absmax8_bits_to_block(m);  // all 32 lanes take part in the shuffles
-        float vs_new = 0.0f;
-        if (KIND == QF_KIND_BLOCK) vs_new = absmax8_bits_to_block(v);
-        if (nv == 0) continue;
-        store_codes(mc, e, nv, vec, quantize8(m, ms_new, s.mm, nv));
-        uint32_t w = 0;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const float sv = KIND == QF_KIND_BLOCK ? vs_new : sc_new[k];
-            const uint32_t c = search16(scaled(v[k], sv), s.mv);
-            w |= (k < nv ? c : 0u) << (4 * k);
-        }
-        store_codes(vc, e, nv, vec, w);
-        if ((lane & 15) == 0) {
-            t.ms[e >> 7] = ms_new;
-            if (KIND == QF_KIND_BLOCK) t.vs[e >> 7] = vs_new;
-            if (nonfinite(ms_new) || nonfinite(vs_new)) atomicOr(status, QF_STATUS_NONFINITE);
-        }
+        if (KIND != QF_KIND_RANK1 && hd.fast && vec && wbase + kPanelCols <= t.numel)
+            main_flat_run_fast<T, KIND>(t, wbase, h2, s, status);
+        else
+            main_flat_run_exact<T, KIND>(tp, wbase, hd, s, status);
     }
 }
 
 // =================================================================================================
-// Multi-tensor kernels
+// Multi-tensor kernels.  `base` is the prefix-sum table of the mapping the kernel serves; tensors of
+// the other mapping have zero items in it.
 // =================================================================================================
 
-__global__ void __launch_bounds__(kThreads)
-step_pre_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict__ base, int n, HyperPack hp,
-                uint32_t* status) {
-    __shared__ Tables s;
-    load_tables(s);
+template <bool PANEL>
+__global__ void __launch_bounds__(kThreads, 3)
+step_pre_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict__ base, int n,
+                const __grid_constant__ HyperPack hp, uint32_t* status) {
+    __shared__ Smem s;
+    load_smem(s);
     const int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
     if (item >= base[n]) return;
     const int ti = find_tensor(base, n, item);
     const DevTensor t = tensors[ti];
     const int64_t li = item - base[ti];
-    const QfHyper& h = hp.h[t.hyper];
-    if (t.flags & kFlagPanel) {
+    const HyperDev& h = hp.h[t.hyper];
+    if (PANEL) {
         if (t.dtype == QF_BF16)
             pre_panel<__nv_bfloat16>(t, li, h, s, status);
         else
@@ -355,54 +779,69 @@ step_pre_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict
 }
 
 template <typename T>
-__device__ __forceinline__ void main_dispatch(const DevTensor& t, int64_t li, const QfHyper& h, const Tables& s,
-                                              uint32_t* status) {
-    if (t.kind == QF_KIND_RANK1) {
-        if (t.flags & kFlagPanel)
-            main_panel<T>(t, li, h, s, status);
-        else
-            main_flat<T, QF_KIND_RANK1>(t, li, h, s, status);
-    } else if (t.kind == QF_KIND_BLOCK) {
-        main_flat<T, QF_KIND_BLOCK>(t, li, h, s, status);
-    } else {
-        main_flat<T, QF_KIND_FP32>(t, li, h, s, status);
-    }
+__device__ __forceinline__ void main_flat_dispatch(const DevTensor* tp, int64_t li, const HyperDev& h, const Smem& s,
+                                                   uint32_t* status) {
+    const int kind = tp->kind;
+    if (kind == QF_KIND_RANK1)
+        main_flat<T, QF_KIND_RANK1>(tp, li, h, s, status);
+    else if (kind == QF_KIND_BLOCK)
+        main_flat<T, QF_KIND_BLOCK>(tp, li, h, s, status);
+    else
+        main_flat<T, QF_KIND_FP32>(tp, li, h, s, status);
 }
 
-__global__ void __launch_bounds__(kThreads)
-step_main_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict__ base, int n, HyperPack hp,
-                 uint32_t* status) {
-    __shared__ Tables s;
-    load_tables(s);
+#ifndef QF_MAIN_MIN_CTAS
+#define QF_MAIN_MIN_CTAS 2
+#endif
+template <bool PANEL>
+__global__ void __launch_bounds__(kThreads, QF_MAIN_MIN_CTAS)
+step_main_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict__ base, int n,
+                 const __grid_constant__ HyperPack hp, uint32_t* status) {
+    __shared__ Smem s;
+    load_smem(s);
     const int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
     if (item >= base[n]) return;
     const int ti = find_tensor(base, n, item);
-    const DevTensor t = tensors[ti];
+    const DevTensor* tp = tensors + ti;
     const int64_t li = item - base[ti];
-    const QfHyper& h = hp.h[t.hyper];
-    if (t.dtype == QF_BF16)
-        main_dispatch<__nv_bfloat16>(t, li, h, s, status);
-    else
-        main_dispatch<float>(t, li, h, s, status);
+    const HyperDev& h = hp.h[tp->hyper];  // hp is a grid constant: its address is usable as it is
+    if (PANEL) {
+        extern __shared__ __align__(16) char staging[];  // kMainDynSmem bytes: one ring per warp
+        char* stage = staging + (threadIdx.x >> 5) * (kStages * kStageRowBytesMax);
+        if (tp->dtype == QF_BF16)
+            main_panel<__nv_bfloat16>(tp, li, h, s, stage, status);
+        else
+            main_panel<float>(tp, li, h, s, stage, status);
+    } else {
+        if (tp->dtype == QF_BF16)
+            main_flat_dispatch<__nv_bfloat16>(tp, li, h, s, status);
+        else
+            main_flat_dispatch<float>(tp, li, h, s, status);
+    }
 }
 
 // One tensor passed by value (the single-tensor entry points that mirror the reference's per-tensor
 // calls).  Block-128 and fp32-state kinds only; the non-finite flag goes to a word nobody reads.
 __device__ uint32_t g_unread_status;
-__global__ void __launch_bounds__(kThreads) single_tensor_kernel(DevTensor t, QfHyper h) {
-    __shared__ Tables s;
-    load_tables(s);
+__global__ void __launch_bounds__(kThreads)
+single_tensor_kernel(const __grid_constant__ DevTensor t, const __grid_constant__ HyperDev h) {
+    __shared__ Smem s;
+    load_smem(s);
     const int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
     if (item * (kPanelCols * kRowsPerItem) >= t.numel) return;
     if (t.dtype == QF_BF16)
-        main_dispatch<__nv_bfloat16>(t, item, h, s, &g_unread_status);
+        main_flat_dispatch<__nv_bfloat16>(&t, item, h, s, &g_unread_status);
     else
-        main_dispatch<float>(t, item, h, s, &g_unread_status);
+        main_flat_dispatch<float>(&t, item, h, s, &g_unread_status);
 }
 
-// mode 0: clear the scratch maxima of every rank-1 tensor; mode 1: copy them over the stored maxima.
-// One CTA per (tensor, slice); tensors that are not rank-1 exit at once.
+// Small passes over the row / column maxima of every rank-1 tensor.  One CTA per (tensor, slice).
+//   kRollClear     new maxima := 0                       (before the first pass)
+//   kRollRecip     reciprocals of the new maxima         (between the passes; 0 for a zero maximum, NaN
+//                  where the old or the new maximum is outside the range of the fast division)
+//   kRollCommit    stored maxima := new maxima           (after the second pass)
 constexpr int kRollSlices = 4;
+enum { kRollClear = 0, kRollRecip = 1, kRollCommit = 2 };
 __global__ void __launch_bounds__(kThreads)
 rank1_roll_kernel(const DevTensor* __restrict__ tensors, int n, int mode) {
     const int ti = blockIdx.x / kRollSlices;
@@ -411,12 +850,18 @@ rank1_roll_kernel(const DevTensor* __restrict__ tensors, int n, int mode) {
     if (t.kind != QF_KIND_RANK1) return;
     const int total = t.rows + t.cols;
     for (int i = (blockIdx.x % kRollSlices) * kThreads + threadIdx.x; i < total; i += kRollSlices * kThreads) {
-        float* nw = i < t.rows ? t.vrow_new + i : t.vcol_new + (i - t.rows);
-        if (mode == 0) {
-            *nw = 0.0f;
+        const bool is_row = i < t.rows;
+        const int k = is_row ? i : i - t.rows;
+        float* nw = is_row ? t.vrow_new : t.vcol_new;
+        const int len = is_row ? t.rows : t.cols;
+        if (mode == kRollClear) {
+            nw[k] = 0.0f;
+        } else if (mode == kRollRecip) {
+            const float x = nw[k], old = (is_row ? t.vs : t.vcol)[k];
+            const float r = x == 0.0f ? 0.0f : __frcp_rn(x);
+            nw[len + k] = scale_safe(x) && scale_safe(old) ? r : __uint_as_float(0x7fc00000u);
         } else {
-            float* old = i < t.rows ? t.vs + i : t.vcol + (i - t.rows);
-            *old = *nw;
+            (is_row ? t.vs : t.vcol)[k] = nw[k];
         }
     }
 }
@@ -429,9 +874,9 @@ rank1_roll_kernel(const DevTensor* __restrict__ tensors, int n, int mode) {
 __global__ void __launch_bounds__(kThreads)
 quantize_block_kernel(const float* __restrict__ x, int64_t numel, int map, uint8_t* __restrict__ codes,
                       float* __restrict__ scales, int vec) {
-    __shared__ Tables s;
-    load_tables(s);
-    const float* mid = map ? s.mv : s.mm;
+    __shared__ Smem s;
+    load_smem(s);
+    const float* mid = map ? s.t.mv : s.t.mm;
     const int lane = threadIdx.x & 31;
     const int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
     const int64_t start = item * (kPanelCols * kRowsPerItem);
@@ -443,9 +888,21 @@ quantize_block_kernel(const float* __restrict__ x, int64_t numel, int map, uint8
         float v[8];
         load8_masked<float>(reinterpret_cast<const char*>(x), e, nv, vec, v);
         const float sc = absmax8_bits_to_block(v);
-        if (nv == 0) continue;
-        store_codes(codes, e, nv, vec, quantize8(v, sc, mid, nv));
-        if ((lane & 15) == 0) scales[e >> 7] = sc;
+        if (vec && wbase + kPanelCols <= numel && scale_safe(sc)) {  // full run: packed division, table search
+            const f2 r2 = bc2(sc == 0.0f ? 0.0f : __frcp_rn(sc)), ns2 = bc2(-sc);
+            uint32_t w = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const f2 q = div2_prepared(mk2(v[2 * j], v[2 * j + 1]), r2, ns2);
+                const uint32_t c0 = map ? search_v_closed(q.x) : search_m_lut(q.x, s.mlut);
+                const uint32_t c1 = map ? search_v_closed(q.y) : search_m_lut(q.y, s.mlut);
+                w |= (c0 << (8 * j)) | (c1 << (8 * j + 4));
+            }
+            *reinterpret_cast<uint32_t*>(codes + (e >> 1)) = w;
+        } else if (nv) {
+            store_codes(codes, e, nv, vec, quantize8(v, sc, mid, nv));
+        }
+        if (nv && (lane & 15) == 0) scales[e >> 7] = sc;
     }
 }
 
@@ -472,7 +929,7 @@ dequantize_block_kernel(const uint8_t* __restrict__ codes, const float* __restri
 }
 
 // Row / column maxima of |v| for an [R, C] fp32 matrix.  panel != 0: C is a multiple of 256 and the
-// buffers are vector-aligned; otherwise one thread per element group with per-element atomics.
+// buffers are vector-aligned; otherwise per-element atomics.
 __global__ void __launch_bounds__(kThreads)
 rank1_max_kernel(const float* __restrict__ v, int rows, int cols, float* __restrict__ row_max,
                  float* __restrict__ col_max, int panel) {

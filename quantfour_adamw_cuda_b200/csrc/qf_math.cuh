@@ -1,0 +1,112 @@
+// Packed-fp32 arithmetic of the fast path (sm_100a): every add / multiply / fused multiply-add works on
+// two elements per instruction (fma.rn.f32x2 and friends), and the IEEE divisions and square roots of the
+// reference arithmetic are produced by explicit Newton / Markstein sequences built from those packed
+// operations plus one MUFU approximation, instead of the general-purpose div.rn / sqrt.rn expansions.
+//
+// Each sequence returns the correctly rounded (round-to-nearest-even) result for operands in the ranges
+// the callers guarantee; outside those ranges the callers take the exact path of qf_device.cuh:
+//   sqrt2      any v >= 0 (operands below 2^-96, where the residual of the Newton step would underflow,
+//              branch to sqrt.rn inside the function)
+//   div2       divisor normal, in [2^-90, 2^100]; dividend 0 or of magnitude >= 2^-100
+//   Recip      the same ranges; the reciprocal is shared by all dividends of one divisor
+// The test-suite checks sqrt2 against sqrt.rn on every non-negative float and the division sequences
+// against div.rn on billions of random and structured operand pairs (tests/cuda/math_check.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace qf {
+
+using f2 = float2;
+
+__device__ __forceinline__ f2 mk2(float a, float b) { return make_float2(a, b); }
+__device__ __forceinline__ f2 bc2(float a) { return make_float2(a, a); }
+// The packed operations are written as PTX with an explicit .rn.  CAUTION: ptxas 12.9 was observed to
+// contract a packed multiply whose only use is a packed add into one packed fused multiply-add even so
+// (found with a device-side check against mul.rn + add.rn), which changes the rounding.  No sequence in this library feeds a
+// mul2 result into add2; where the reference arithmetic has "round(a*b) then add", the product is taken as
+// fma2(a, b, 0), which rounds identically and cannot be merged with the following add.
+__device__ __forceinline__ unsigned long long as_u64(f2 a) {
+    return (static_cast<unsigned long long>(__float_as_uint(a.y)) << 32) | __float_as_uint(a.x);
+}
+__device__ __forceinline__ f2 as_f2(unsigned long long u) {
+    return make_float2(__uint_as_float(static_cast<unsigned>(u)), __uint_as_float(static_cast<unsigned>(u >> 32)));
+}
+__device__ __forceinline__ f2 mul2(f2 a, f2 b) {
+    unsigned long long d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(as_u64(a)), "l"(as_u64(b)));
+    return as_f2(d);
+}
+__device__ __forceinline__ f2 add2(f2 a, f2 b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(as_u64(a)), "l"(as_u64(b)));
+    return as_f2(d);
+}
+__device__ __forceinline__ f2 fma2(f2 a, f2 b, f2 c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(as_u64(a)), "l"(as_u64(b)), "l"(as_u64(c)));
+    return as_f2(d);
+}
+__device__ __forceinline__ f2 neg2(f2 a) { return mul2(a, bc2(-1.0f)); }  // exact
+
+__device__ __forceinline__ float rsqrt_approx(float x) {
+    float y;
+    asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+constexpr float kFltMin = 1.17549435e-38f;
+
+// Correctly rounded sqrt of two non-negative values.  y ~ 1/sqrt(v); s = v*y; one Newton step with
+// the residual taken exactly by a fused multiply-add: s + (v - s*s) * (y/2).  The residual is a multiple
+// of ulp(s)^2, representable only while v >= 2^-103; smaller operands (zero included) take sqrt.rn.
+// CHECKED = false is for callers that know both operands are >= 2^-96.
+template <bool CHECKED = true>
+__device__ __forceinline__ f2 sqrt2(f2 v) {
+    if (CHECKED && fminf(v.x, v.y) < 0x1p-96f) return mk2(__fsqrt_rn(v.x), __fsqrt_rn(v.y));
+    const f2 y = mk2(rsqrt_approx(v.x), rsqrt_approx(v.y));
+    const f2 s = mul2(v, y);
+    const f2 nh = mul2(y, bc2(-0.5f));
+    const f2 e = fma2(s, s, neg2(v));  // s*s - v
+    return fma2(e, nh, s);
+}
+
+// A divisor prepared for repeated division: r ~ 1/d (MUFU + one Newton step), nd = -d.
+struct Recip {
+    float r, nd;
+};
+__device__ __forceinline__ Recip make_recip(float d) {
+    Recip o;
+    o.nd = -d;
+    const float r0 = d == 0.0f ? 0.0f : rcp_approx(d);  // d == 0: every dividend is 0 as well -> quotient 0
+    const float e = __fmaf_rn(o.nd, r0, 1.0f);
+    o.r = __fmaf_rn(r0, e, r0);
+    return o;
+}
+
+// a / d for two dividends and per-element divisors given as (r, nd): quotient estimate and two
+// residual corrections, each residual exact through the fused multiply-add.
+__device__ __forceinline__ f2 div2_prepared(f2 a, f2 r, f2 nd) {
+    f2 q = mul2(a, r);
+    f2 t = fma2(nd, q, a);
+    q = fma2(t, r, q);
+    t = fma2(nd, q, a);
+    return fma2(t, r, q);
+}
+
+// a / d for two independent (dividend, divisor) pairs.
+__device__ __forceinline__ f2 div2(f2 a, f2 d) {
+    const f2 nd = neg2(d);
+    const f2 r0 = mk2(rcp_approx(d.x), rcp_approx(d.y));
+    const f2 e = fma2(nd, r0, bc2(1.0f));
+    const f2 r = fma2(r0, e, r0);
+    return div2_prepared(a, r, nd);
+}
+
+}  // namespace qf

@@ -145,7 +145,9 @@ class FourBitAdamW(torch.optim.Optimizer):
         s = self._scratch.get(p)
         if s is None or s[0].device != p.device:
             R, Cc = p.shape
-            s = (torch.zeros(R, dtype=torch.float32, device=p.device), torch.zeros(Cc, dtype=torch.float32, device=p.device))
+            # new maxima followed by their reciprocals (the layout qf_step_multi expects)
+            s = (torch.zeros(2 * R, dtype=torch.float32, device=p.device),
+                 torch.zeros(2 * Cc, dtype=torch.float32, device=p.device))
             self._scratch[p] = s
         return s
 

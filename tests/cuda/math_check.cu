@@ -1,0 +1,179 @@
+// Device-side checks of the packed fast-path arithmetic (quantfour_adamw_cuda_b200/csrc/qf_math.cuh and the
+// table / closed-form searches of qf_kernels.cuh) against the plain IEEE intrinsics and the 4-step binary
+// search.  Test infrastructure: built into tests/cuda/libqf_mathcheck.so, loaded only by the test-suite.
+#include <cstdint>
+#include <cstdio>
+
+#include "../../quantfour_adamw_cuda_b200/csrc/qf_kernels.cuh"
+
+namespace {
+
+struct Report {
+    unsigned long long checked, bad;
+    unsigned int first_a, first_b;
+};
+
+__device__ void note(Report* r, uint32_t a, uint32_t b) {
+    if (atomicAdd(&r->bad, 1ull) == 0) {
+        r->first_a = a;
+        r->first_b = b;
+    }
+}
+
+// sqrt2 against sqrt.rn for every float bit pattern in [lo, hi).
+__global__ void k_sqrt(uint32_t lo, uint64_t count, Report* r) {
+    for (uint64_t i = (blockIdx.x * (uint64_t)blockDim.x + threadIdx.x) * 2; i < count; i += (uint64_t)gridDim.x * blockDim.x * 2) {
+        const float a = __uint_as_float(lo + (uint32_t)i), b = __uint_as_float(lo + (uint32_t)i + 1);
+        const qf::f2 s = qf::sqrt2(qf::mk2(a, b));
+        if (__float_as_uint(s.x) != __float_as_uint(__fsqrt_rn(a))) note(r, __float_as_uint(a), __float_as_uint(s.x));
+        if (i + 1 < count && __float_as_uint(s.y) != __float_as_uint(__fsqrt_rn(b))) note(r, __float_as_uint(b), __float_as_uint(s.y));
+    }
+}
+
+__device__ uint64_t splitmix(uint64_t& x) {
+    uint64_t z = (x += 0x9e3779b97f4a7c15ull);
+    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+    z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+    return z ^ (z >> 31);
+}
+
+// A float with random sign (if sgn), random mantissa and an exponent drawn from [emin, emax] (unbiased).
+__device__ float rnd_float(uint64_t& st, int emin, int emax, bool sgn, int mant_mode) {
+    const uint64_t z = splitmix(st);
+    uint32_t mant = (uint32_t)z & 0x7fffffu;
+    if (mant_mode == 1) mant = 0x7fffffu - ((uint32_t)(z >> 40) & 0xffu);   // mantissa near all ones
+    if (mant_mode == 2) mant = (uint32_t)(z >> 40) & 0xffu;                  // mantissa near zero
+    const int e = emin + (int)((z >> 23) % (uint64_t)(emax - emin + 1));
+    uint32_t bits = ((uint32_t)(e + 127) << 23) | mant;
+    if (sgn && (z >> 63)) bits |= 0x80000000u;
+    return __uint_as_float(bits);
+}
+
+// mode 0: div2 (independent divisors, MUFU reciprocal);  mode 1: div2_prepared with r = rcp.rn(d);
+// mode 2: div2_prepared with r = RN(1/d) and a restricted dividend range (|a| <= d, the quantize case).
+__global__ void k_div(uint64_t seed, uint64_t per_thread, int mode, int a_emin, int a_emax, int d_emin, int d_emax,
+                      int mant_mode, Report* r) {
+    uint64_t st = seed ^ ((blockIdx.x * (uint64_t)blockDim.x + threadIdx.x) * 0x2545f4914f6cdd1dull);
+    for (uint64_t i = 0; i < per_thread; ++i) {
+        const float d0 = rnd_float(st, d_emin, d_emax, false, mant_mode), d1 = rnd_float(st, d_emin, d_emax, false, mant_mode);
+        float a0 = rnd_float(st, a_emin, a_emax, true, (int)(i & 1) * mant_mode), a1 = rnd_float(st, a_emin, a_emax, true, 0);
+        if (mode == 2) {
+            a0 = a0 * d0;
+            a1 = a1 * d1;
+        }
+        qf::f2 q;
+        if (mode == 0) {
+            q = qf::div2(qf::mk2(a0, a1), qf::mk2(d0, d1));
+        } else {
+            q = qf::div2_prepared(qf::mk2(a0, a1), qf::mk2(__frcp_rn(d0), __frcp_rn(d1)), qf::mk2(-d0, -d1));
+        }
+        if (__float_as_uint(q.x) != __float_as_uint(__fdiv_rn(a0, d0))) note(r, __float_as_uint(a0), __float_as_uint(d0));
+        if (__float_as_uint(q.y) != __float_as_uint(__fdiv_rn(a1, d1))) note(r, __float_as_uint(a1), __float_as_uint(d1));
+    }
+}
+
+// "round(a*b), then add c" written the way the kernels write it -- fma2(a, b, 0) followed by add2 -- must
+// round twice like mul.rn + add.rn.
+__global__ void k_nofuse(uint64_t seed, uint64_t per_thread, Report* r) {
+    uint64_t st = seed ^ ((blockIdx.x * (uint64_t)blockDim.x + threadIdx.x) * 0x2545f4914f6cdd1dull);
+    for (uint64_t i = 0; i < per_thread; ++i) {
+        const float a0 = rnd_float(st, -8, 0, true, 0), a1 = rnd_float(st, -8, 0, true, 0);
+        const float b0 = rnd_float(st, -1, 0, false, 0), b1 = rnd_float(st, -1, 0, false, 0);
+        const float c0 = rnd_float(st, -12, -6, true, 0), c1 = rnd_float(st, -12, -6, true, 0);
+        const qf::f2 d = qf::add2(qf::fma2(qf::mk2(a0, a1), qf::mk2(b0, b1), qf::bc2(0.0f)), qf::mk2(c0, c1));
+        if (__float_as_uint(d.x) != __float_as_uint(__fadd_rn(__fmul_rn(a0, b0), c0))) note(r, __float_as_uint(a0), __float_as_uint(b0));
+        if (__float_as_uint(d.y) != __float_as_uint(__fadd_rn(__fmul_rn(a1, b1), c1))) note(r, __float_as_uint(a1), __float_as_uint(b1));
+    }
+}
+
+// Both searches against the 4-step binary search for every float bit pattern.
+__global__ void k_search(Report* r) {
+    __shared__ qf::Smem s;
+    qf::load_smem(s);
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < (1ull << 32); i += (uint64_t)gridDim.x * blockDim.x) {
+        const float x = __uint_as_float((uint32_t)i);
+        if (x != x) continue;  // NaN is outside the contract of the fast searches
+        if (qf::search_m_lut(x, s.mlut) != qf::search16(x, s.t.mm)) note(r, (uint32_t)i, 0);
+        if (qf::search_v_closed(x) != qf::search16(x, s.t.mv)) note(r, (uint32_t)i, 1);
+    }
+}
+
+// Code -> value reconstruction of the fast dequantize: (2^23 + c) - (2^23 - 1) = c + 1 and (c + 1) * (s / 16)
+// against qv[c] * s, for all 16 codes and `count` scale bit patterns from `lo` on.
+__global__ void k_dequant_v(uint32_t lo, uint64_t count, Report* r) {
+    __shared__ qf::Smem s;
+    qf::load_smem(s);
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < count * 16; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t c = (uint32_t)(i & 15);
+        const float sc = __uint_as_float(lo + (uint32_t)(i >> 4));
+        if (!qf::scale_safe(sc)) continue;
+        const float fast = __fmul_rn(__fadd_rn(qf::code_plus_2p23(c, 0), qf::kMagic), sc * 0.0625f);
+        if (__float_as_uint(fast) != __float_as_uint(__fmul_rn(s.t.qv[c], sc))) note(r, c, __float_as_uint(sc));
+    }
+}
+
+int finish(Report* d, unsigned long long* checked_bad, unsigned int* first) {
+    Report h;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(&h, d, sizeof h, cudaMemcpyDeviceToHost);
+    cudaFree(d);
+    if (e != cudaSuccess) {
+        fprintf(stderr, "math_check: %s\n", cudaGetErrorString(e));
+        return 1;
+    }
+    checked_bad[0] = h.bad;
+    first[0] = h.first_a;
+    first[1] = h.first_b;
+    return 0;
+}
+
+Report* fresh() {
+    Report* d = nullptr;
+    if (cudaMalloc(&d, sizeof(Report)) != cudaSuccess) return nullptr;
+    cudaMemset(d, 0, sizeof(Report));
+    return d;
+}
+
+}  // namespace
+
+extern "C" {
+
+int qfc_sqrt(uint32_t lo_bits, uint64_t count, unsigned long long* bad, unsigned int* first) {
+    Report* d = fresh();
+    if (!d) return 1;
+    k_sqrt<<<148 * 8, 256>>>(lo_bits, count, d);
+    return finish(d, bad, first);
+}
+
+int qfc_div(uint64_t seed, uint64_t per_thread, int mode, int a_emin, int a_emax, int d_emin, int d_emax, int mant_mode,
+            unsigned long long* bad, unsigned int* first) {
+    Report* d = fresh();
+    if (!d) return 1;
+    k_div<<<148 * 8, 256>>>(seed, per_thread, mode, a_emin, a_emax, d_emin, d_emax, mant_mode, d);
+    return finish(d, bad, first);
+}
+
+int qfc_nofuse(uint64_t seed, uint64_t per_thread, unsigned long long* bad, unsigned int* first) {
+    Report* d = fresh();
+    if (!d) return 1;
+    k_nofuse<<<148 * 8, 256>>>(seed, per_thread, d);
+    return finish(d, bad, first);
+}
+
+int qfc_search(unsigned long long* bad, unsigned int* first) {
+    Report* d = fresh();
+    if (!d) return 1;
+    k_search<<<148 * 4, 256>>>(d);
+    return finish(d, bad, first);
+}
+
+int qfc_dequant_v(uint32_t lo_bits, uint64_t count, unsigned long long* bad, unsigned int* first) {
+    Report* d = fresh();
+    if (!d) return 1;
+    k_dequant_v<<<148 * 8, 256>>>(lo_bits, count, d);
+    return finish(d, bad, first);
+}
+
+int qfc_threads(void) { return 148 * 8 * 256; }
+
+}  // extern "C"

@@ -24,8 +24,8 @@ class GpuState:
         self.device = torch.device(device)
         self.load(st)
         if self.kind == "rank1":
-            self.row_new = torch.zeros(self.shape[0], device=device)
-            self.col_new = torch.zeros(self.shape[1], device=device)
+            self.row_new = torch.zeros(2 * self.shape[0], device=device)
+            self.col_new = torch.zeros(2 * self.shape[1], device=device)
 
     def load(self, st: TO.TensorState) -> None:
         """Overwrite the device state with the oracle's (teacher forcing)."""

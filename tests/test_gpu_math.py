@@ -1,0 +1,65 @@
+"""GPU checks of the fast-path arithmetic against the IEEE intrinsics (tests/cuda/math_check.cu):
+sqrt on every non-negative normal float, the division sequences on random and structured operands,
+both code searches on every float, and the mantissa-trick dequantize on a sweep of scales."""
+import ctypes as C
+import os
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, "cuda"))
+
+
+@pytest.fixture(scope="module")
+def mc():
+    import build_mathcheck
+    lib = C.CDLL(build_mathcheck.build())
+    return lib
+
+
+def _call(fn, *args):
+    bad = (C.c_ulonglong * 1)()
+    first = (C.c_uint * 2)()
+    assert fn(*args, bad, first) == 0
+    return bad[0], (hex(first[0]), hex(first[1]))
+
+
+def test_sqrt_sequence_is_correctly_rounded_on_every_nonnegative_float(mc):
+    # zero, denormals and normals: every finite bit pattern 0 .. 0x7f7fffff
+    bad, first = _call(mc.qfc_sqrt, C.c_uint32(0), C.c_uint64(0x7f800000))
+    assert bad == 0, first
+
+
+@pytest.mark.parametrize("mode,a_rng,d_rng", [
+    (0, (-40, 10), (-30, 20)),      # update / denominator: den >= eps, numerator small
+    (0, (-60, 60), (-60, 60)),      # wide; quotients stay normal (the sequences are not meant for denormal results)
+    (1, (-25, 25), (-90, 100)),     # prepared reciprocal, wide
+    (2, (-9, -1), (-90, 90)),       # quantize: |a| <= d, down to the smallest midpoint
+    (2, (-30, -1), (-60, 90)),
+])
+@pytest.mark.parametrize("mant_mode", [0, 1, 2])
+def test_division_sequences_match_div_rn(mc, mode, a_rng, d_rng, mant_mode):
+    per_thread = 4000
+    bad, first = _call(mc.qfc_div, C.c_uint64(1234 + 17 * mode + mant_mode), C.c_uint64(per_thread), mode,
+                       a_rng[0], a_rng[1], d_rng[0], d_rng[1], mant_mode)
+    assert bad == 0, (first, "of", 2 * per_thread * mc.qfc_threads())
+
+
+def test_product_taken_as_fma_with_zero_then_add_rounds_twice(mc):
+    bad, first = _call(mc.qfc_nofuse, C.c_uint64(99), C.c_uint64(2000))
+    assert bad == 0, first
+
+
+def test_searches_match_binary_search_on_every_float(mc):
+    bad, first = _call(mc.qfc_search)
+    assert bad == 0, first
+
+
+def test_mantissa_trick_dequantize_matches_table_times_scale(mc):
+    bad, first = _call(mc.qfc_dequant_v, C.c_uint32(0x12000000), C.c_uint64(1 << 26))   # scales from 2^-91 up
+    assert bad == 0, first
+    bad, first = _call(mc.qfc_dequant_v, C.c_uint32(0x2f000000), C.c_uint64(1 << 28))   # around 1e-10 .. 1e-1
+    assert bad == 0, first
