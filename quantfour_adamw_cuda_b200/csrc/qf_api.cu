@@ -112,7 +112,7 @@ int build_plan(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* wor
             t.ms = d.m_scale;
             t.vs = d.v_scale;
         }
-        int64_t items = flat_items(d.numel);
+        int64_t items = flat_items(d.numel), pre_items = items;
         if (d.kind == QF_KIND_RANK1) {
             if (d.rows <= 0 || d.cols <= 0 || d.rows * d.cols != d.numel || d.rows > INT32_MAX || d.cols > INT32_MAX)
                 return fail(QF_ERR_BAD_ARG, "tensor %d: rows*cols must equal numel (rows=%lld cols=%lld numel=%lld)", i,
@@ -130,6 +130,7 @@ int build_plan(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* wor
                 t.flags |= qf::kFlagPanel;
                 t.panels = static_cast<int32_t>(d.cols / qf::kPanelCols);
                 items = (d.rows + qf::kRowsPerItem - 1) / qf::kRowsPerItem * t.panels;
+                pre_items = (d.rows + qf::kPreRowsPerItem - 1) / qf::kPreRowsPerItem * t.panels;
             }
             ++n_rank1;
         }
@@ -137,8 +138,8 @@ int build_plan(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* wor
         const bool panel = t.flags & qf::kFlagPanel, rank1 = d.kind == QF_KIND_RANK1;
         base[kMainPanel].push_back(base[kMainPanel].back() + (panel ? items : 0));
         base[kMainFlat].push_back(base[kMainFlat].back() + (panel ? 0 : items));
-        base[kPrePanel].push_back(base[kPrePanel].back() + (rank1 && panel ? items : 0));
-        base[kPreFlat].push_back(base[kPreFlat].back() + (rank1 && !panel ? items : 0));
+        base[kPrePanel].push_back(base[kPrePanel].back() + (rank1 && panel ? pre_items : 0));
+        base[kPreFlat].push_back(base[kPreFlat].back() + (rank1 && !panel ? pre_items : 0));
         tab.push_back(t);
     }
     const int n = static_cast<int>(tab.size());

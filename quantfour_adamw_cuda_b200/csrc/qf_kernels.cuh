@@ -273,8 +273,8 @@ __device__ __forceinline__ void pre_panel(const DevTensor& t, int64_t li, const 
     const int lane = threadIdx.x & 31;
     const int band = static_cast<int>(li / t.panels);
     const int panel = static_cast<int>(li - static_cast<int64_t>(band) * t.panels);
-    const int r0 = band * kRowsPerItem;
-    const int r1 = min(r0 + kRowsPerItem, t.rows);
+    const int r0 = band * kPreRowsPerItem;
+    const int r1 = min(r0 + kPreRowsPerItem, t.rows);
     const int j0 = panel * kPanelCols + lane * 8;
     float col_old[8];
     load8f(t.vcol, j0, col_old);
@@ -379,11 +379,14 @@ __device__ __noinline__ void main_panel_row_exact(const DevTensor* tp, int64_t e
 // Each lane copies its own 16-byte pieces of p and g and its two code words of the rows ahead into a
 // per-warp ring in shared memory with cp.async and reads them back when their row comes up.  A lane only
 // ever reads what it copied itself, so the ring needs no barrier: cp.async.wait_group orders a lane's
-// copies with its own reads.  kStages - 1 rows are in flight per warp, which holds enough bytes in flight
-// per SM to cover HBM latency at two CTAs per SM without spending registers on it.
-constexpr int kStages = 4;
-constexpr int kStageRowBytesMax = 32 * (2 * 2 * 16 + 8);            // fp32 parameters: 2304 bytes per row
-constexpr int kMainDynSmem = kWarpsPerCta * kStages * kStageRowBytesMax;
+// copies with its own reads.  The rows in flight per warp (4 for bf16, 2 for fp32 parameters) cover HBM
+// latency at two CTAs per SM without spending registers on it.  The per-lane column maxima (old, new,
+// reciprocal of new) sit in shared memory as well and are fetched pair by pair: registers are the scarce
+// resource of this kernel.
+constexpr int kRingBytes = 3 * 32 * (2 * 2 * 16 + 8);  // per warp: 3 rows of fp32 parameters or 5 rows of bf16
+constexpr int kColBytes = 3 * 4 * 32 * 8;              // per warp: old / new / reciprocal column maxima of its 256 columns
+constexpr int kWarpDynSmem = kRingBytes + kColBytes;
+constexpr int kMainDynSmem = kWarpsPerCta * kWarpDynSmem;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<unsigned>(__cvta_generic_to_shared(smem))),
@@ -417,6 +420,8 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
     constexpr int NV = sizeof(T) / 2;  // 16-byte vectors per lane and array: 1 (bf16) or 2 (fp32)
     constexpr int kArr = NV * 512;     // bytes of one staged array of one row
     constexpr int kRowBytes = 2 * kArr + 256;
+    constexpr int kStages = kRingBytes / kRowBytes;
+    static_assert(kStages >= 3, "ring too small");
     auto issue = [&](int r, int slot) {
         if (r < r1) {
             const int64_t e = static_cast<int64_t>(r) * t.cols + j0;
@@ -434,16 +439,25 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
 #pragma unroll
     for (int i = 0; i < kStages - 1; ++i) issue(r0 + i, i);
 
-    float col_old[8], col_new[8], rcol[8];
-    load8f(t.vcol, j0, col_old);
-    load8f(t.vcol_new, j0, col_new);
-    load8f(t.vcol_new + t.cols, j0, rcol);
     // The pass that stored the reciprocals wrote NaN where an old or new maximum is outside the range of
     // the fast sequences.  A zero old maximum (first step, rows never touched) lets v fall below the range
     // of the unchecked square root, so such rows and columns take the exact path as well.
+    f2* colbuf = reinterpret_cast<f2*>(stage + kRingBytes);  // [old | -new | 1/new][pair][lane]
     bool ok = hd.fast;
+    {
+        float col_old[8], col_new[8], rcol[8];
+        load8f(t.vcol, j0, col_old);
+        load8f(t.vcol_new, j0, col_new);
+        load8f(t.vcol_new + t.cols, j0, rcol);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) ok &= rcol[k] == rcol[k] && col_old[k] > 0.0f;
+        for (int k = 0; k < 8; ++k) ok &= rcol[k] == rcol[k] && col_old[k] > 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            colbuf[(0 * 4 + j) * 32 + lane] = mk2(col_old[2 * j], col_old[2 * j + 1]);
+            colbuf[(1 * 4 + j) * 32 + lane] = mk2(-col_new[2 * j], -col_new[2 * j + 1]);
+            colbuf[(2 * 4 + j) * 32 + lane] = mk2(rcol[2 * j], rcol[2 * j + 1]);
+        }
+    }
     const bool col_fast = __all_sync(kFull, ok);
     const Hyper2 h2 = widen(hd);
 
@@ -489,13 +503,15 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
         for (int j = 0; j < 4; ++j) {
             f2 pp = mk2(p[2 * j], p[2 * j + 1]);
             m[j] = mul2(pair_lookup(s.qm2, wm, j), ms_old);
-            f2 v = mul2(pair_lookup(s.qv2, wv, j), mk2(fminf(row_old, col_old[2 * j]), fminf(row_old, col_old[2 * j + 1])));
+            const f2 co = colbuf[(0 * 4 + j) * 32 + lane], ncn = colbuf[(1 * 4 + j) * 32 + lane],
+                     rcn = colbuf[(2 * 4 + j) * 32 + lane];
+            f2 v = mul2(pair_lookup(s.qv2, wv, j), mk2(fminf(row_old, co.x), fminf(row_old, co.y)));
             adamw_pair<true>(pp, mk2(g[2 * j], g[2 * j + 1]), m[j], v, h2);
             p[2 * j] = pp.x;
             p[2 * j + 1] = pp.y;
             // requantize v: scale = min(row', col') -> -scale = max(-row', -col'), 1/scale = max(1/row', 1/col')
-            const f2 nsv = mk2(fmaxf(-row_new, -col_new[2 * j]), fmaxf(-row_new, -col_new[2 * j + 1]));
-            const f2 rv = mk2(fmaxf(rrow, rcol[2 * j]), fmaxf(rrow, rcol[2 * j + 1]));
+            const f2 nsv = mk2(fmaxf(-row_new, ncn.x), fmaxf(-row_new, ncn.y));
+            const f2 rv = mk2(fmaxf(rrow, rcn.x), fmaxf(rrow, rcn.y));
             const f2 y = fma2(div2_prepared(v, rv, nsv), bc2(16.0f), bc2(-1.5f));
             wq += code_from_y(y.x) << (8 * j);
             wq += code_from_y(y.y) << (8 * j + 4);
@@ -807,7 +823,7 @@ step_main_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restric
     const HyperDev& h = hp.h[tp->hyper];  // hp is a grid constant: its address is usable as it is
     if (PANEL) {
         extern __shared__ __align__(16) char staging[];  // kMainDynSmem bytes: one ring per warp
-        char* stage = staging + (threadIdx.x >> 5) * (kStages * kStageRowBytesMax);
+        char* stage = staging + (threadIdx.x >> 5) * kWarpDynSmem;
         if (tp->dtype == QF_BF16)
             main_panel<__nv_bfloat16>(tp, li, h, s, stage, status);
         else

@@ -22,32 +22,14 @@ using f2 = float2;
 
 __device__ __forceinline__ f2 mk2(float a, float b) { return make_float2(a, b); }
 __device__ __forceinline__ f2 bc2(float a) { return make_float2(a, a); }
-// The packed operations are written as PTX with an explicit .rn.  CAUTION: ptxas 12.9 was observed to
-// contract a packed multiply whose only use is a packed add into one packed fused multiply-add even so
-// (found with a device-side check against mul.rn + add.rn), which changes the rounding.  No sequence in this library feeds a
-// mul2 result into add2; where the reference arithmetic has "round(a*b) then add", the product is taken as
-// fma2(a, b, 0), which rounds identically and cannot be merged with the following add.
-__device__ __forceinline__ unsigned long long as_u64(f2 a) {
-    return (static_cast<unsigned long long>(__float_as_uint(a.y)) << 32) | __float_as_uint(a.x);
-}
-__device__ __forceinline__ f2 as_f2(unsigned long long u) {
-    return make_float2(__uint_as_float(static_cast<unsigned>(u)), __uint_as_float(static_cast<unsigned>(u >> 32)));
-}
-__device__ __forceinline__ f2 mul2(f2 a, f2 b) {
-    unsigned long long d;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(as_u64(a)), "l"(as_u64(b)));
-    return as_f2(d);
-}
-__device__ __forceinline__ f2 add2(f2 a, f2 b) {
-    unsigned long long d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(as_u64(a)), "l"(as_u64(b)));
-    return as_f2(d);
-}
-__device__ __forceinline__ f2 fma2(f2 a, f2 b, f2 c) {
-    unsigned long long d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(as_u64(a)), "l"(as_u64(b)), "l"(as_u64(c)));
-    return as_f2(d);
-}
+// CAUTION: ptxas 12.9 was observed to contract a packed multiply whose only use is a packed add into one
+// packed fused multiply-add (even when both are spelled with an explicit .rn in PTX), which changes the
+// rounding.  No sequence in this library feeds a mul2 result into add2; where the reference arithmetic has
+// "round(a*b) then add", the product is taken as fma2(a, b, 0), which rounds identically and cannot be
+// merged with the following add (checked on the device by the test-suite).
+__device__ __forceinline__ f2 mul2(f2 a, f2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ f2 add2(f2 a, f2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ f2 fma2(f2 a, f2 b, f2 c) { return __ffma2_rn(a, b, c); }
 __device__ __forceinline__ f2 neg2(f2 a) { return mul2(a, bc2(-1.0f)); }  // exact
 
 __device__ __forceinline__ float rsqrt_approx(float x) {
