@@ -162,6 +162,35 @@ int qf_quantize_rank1(const float* v, int64_t rows, int64_t cols, uint8_t* codes
 int qf_dequantize_rank1(const uint8_t* codes, const float* row_max, const float* col_max, int64_t rows,
                         int64_t cols, float* out, int device, void* stream);
 
+/*
+ * One optimizer step on one rank-1 (2-D) tensor without any caller-provided scratch and without any
+ * allocation.  No counterpart in the reference.
+ *
+ * Who this is for: hosts that must not allocate while they step.  A training runtime that has handed all
+ * device memory to its own pool cannot give this library a workspace it did not plan for, and a raw
+ * allocation at that point would either fail or stall the device (device allocations synchronise);
+ * plug-in hosts that only pass tensors through and own no allocator are in the same position.  For them
+ * the scratch qf_step_multi asks for (descriptor table, status word, new row / column maxima and their
+ * reciprocals) lives inside the library, in a device array of QF_NOALLOC_MAX_ROWS_PLUS_COLS * 8 + 1024
+ * bytes (about 1 MiB) that every GPU which loads the library holds until the process ends.
+ *
+ * Limits and rules:
+ *   - rows + cols <= QF_NOALLOC_MAX_ROWS_PLUS_COLS (a little less when rows is not a multiple of 4);
+ *     larger tensors are refused with QF_ERR_BAD_ARG and a message, nothing is launched;
+ *   - the first call on a device looks up the device address of the built-in array; make that first
+ *     call before any stream capture begins;
+ *   - all calls on a device share the one array.  Each call clears what it needs at zero, so leftovers
+ *     from the previous call do no harm, but two calls whose kernels overlap on the GPU (different
+ *     streams, or different threads) race on it: keep calls on one device in one stream order;
+ *   - the function calls no cudaMalloc / cudaFree / cudaMallocHost and nothing that does.
+ * Same arithmetic, same kernels and same in/out buffers as a QF_KIND_RANK1 tensor in qf_step_multi:
+ * v_row [rows] and v_col [cols] hold the old maxima on entry and the new ones on return.
+ */
+#define QF_NOALLOC_MAX_ROWS_PLUS_COLS 131072
+int qf_step_rank1_noalloc(void* p, const void* g, void* m_codes, void* v_codes, float* m_scale,
+                          float* v_row, float* v_col, int64_t rows, int64_t cols, int dtype,
+                          const QfHyper* hyper, int device, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -17,6 +17,7 @@ QF_MAX_HYPERS = 16
 QF_F32, QF_BF16 = 0, 1
 QF_KIND_FP32, QF_KIND_BLOCK, QF_KIND_RANK1 = 0, 1, 2
 QF_STATUS_NONFINITE = 1
+QF_NOALLOC_MAX_ROWS_PLUS_COLS = 131072
 
 
 class QfHyper(C.Structure):
@@ -52,6 +53,7 @@ _SIGNATURES = {
     "qf_quantize_block": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "qf_dequantize_block": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
     "qf_quantize_rank1": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "qf_step_rank1_noalloc": (C.c_int, [C.c_void_p] * 7 + [C.c_int64, C.c_int64, C.c_int, C.POINTER(QfHyper), C.c_int, C.c_void_p]),
     "qf_dequantize_rank1": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int, C.c_void_p]),
 }
 

@@ -2,6 +2,7 @@
 // launches.  The exported functions are declared and documented in include/quantfour_b200.h.
 #include <cmath>
 #include <cstdarg>
+#include <cstddef>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -448,6 +449,119 @@ int qf_dequantize_rank1(const uint8_t* codes, const float* row_max, const float*
         nullptr, const_cast<uint8_t*>(codes), row_max, col_max, static_cast<int>(rows), static_cast<int>(cols), out, vec);
     QF_CUDA(cudaGetLastError());
     return QF_OK;
+}
+
+// ---- the step of one rank-1 tensor for callers that cannot allocate ------------------------------------
+//
+// Scratch of this entry point: a status word, the one-entry descriptor table and the new row / column
+// maxima with their reciprocals.  It lives in this translation unit as a device array; each GPU that loads
+// the library keeps its own copy of it for the life of the process.
+constexpr size_t kNoAllocHeader = 1024;  // status word, tensor record, four two-entry prefix tables
+constexpr size_t kNoAllocBytes = kNoAllocHeader + 8 * static_cast<size_t>(QF_NOALLOC_MAX_ROWS_PLUS_COLS);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mu;
+unsigned char* g_noalloc_ptr[kMaxDevices] = {};  // device address of g_noalloc_scratch, per device
+
+// g_noalloc_scratch names the array in device code only.  Host code needs the address the device knows it
+// by, asked for once per device while that device is current.
+int noalloc_scratch(int device, unsigned char** out) {
+    if (device < 0 || device >= kMaxDevices) return fail(QF_ERR_BAD_ARG, "device ordinal %d out of range", device);
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (!g_noalloc_ptr[device]) {
+        void* ptr = nullptr;
+        QF_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+        g_noalloc_ptr[device] = static_cast<unsigned char*>(ptr);
+    }
+    *out = g_noalloc_ptr[device];
+    return QF_OK;
+}
+}  // namespace
+
+int qf_step_rank1_noalloc(void* p, const void* g, void* m_codes, void* v_codes, float* m_scale, float* v_row,
+                          float* v_col, int64_t rows, int64_t cols, int dtype, const QfHyper* hyper, int device,
+                          void* stream) {
+    g_err[0] = 0;
+    if (!hyper) return fail(QF_ERR_BAD_ARG, "hyper is null");
+    if (dtype != QF_F32 && dtype != QF_BF16) return fail(QF_ERR_BAD_ARG, "bad dtype %d", dtype);
+    if (rows <= 0 || cols <= 0) return fail(QF_ERR_BAD_ARG, "rows and cols must be positive");
+    if (rows + cols > QF_NOALLOC_MAX_ROWS_PLUS_COLS)
+        return fail(QF_ERR_BAD_ARG, "rows + cols = %lld exceeds the built-in scratch (QF_NOALLOC_MAX_ROWS_PLUS_COLS = %d); use qf_step_multi with caller-owned scratch",
+                    (long long)(rows + cols), QF_NOALLOC_MAX_ROWS_PLUS_COLS);
+    if (!p || !g || !m_codes || !v_codes || !m_scale || !v_row || !v_col) return fail(QF_ERR_BAD_ARG, "null pointer");
+    const size_t esz = dtype == QF_BF16 ? 2 : 4;
+    if (!aligned(p, esz) || !aligned(g, esz) || !aligned(m_scale, 4) || !aligned(v_row, 4) || !aligned(v_col, 4))
+        return fail(QF_ERR_BAD_ARG, "buffer not element-aligned");
+    QF_CUDA(cudaSetDevice(device));
+    unsigned char* scratch = nullptr;
+    if (int rc = noalloc_scratch(device, &scratch)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    // layout: [status | tensor record | 4 prefix tables][row maxima, reciprocals][column maxima, reciprocals]
+    float* row_new = reinterpret_cast<float*>(scratch + kNoAllocHeader);
+    float* col_new = row_new + 2 * ((rows + 3) / 4 * 4);  // keeps the column part 16-byte aligned
+    if (reinterpret_cast<unsigned char*>(col_new + 2 * cols) > scratch + kNoAllocBytes)
+        return fail(QF_ERR_BAD_ARG, "rows + cols too large for the built-in scratch after alignment padding");
+
+    qf::DevTensor t;
+    memset(&t, 0, sizeof t);
+    t.p = static_cast<char*>(p);
+    t.g = static_cast<const char*>(g);
+    t.m = static_cast<char*>(m_codes);
+    t.v = static_cast<char*>(v_codes);
+    t.ms = m_scale;
+    t.vs = v_row;
+    t.vcol = v_col;
+    t.vrow_new = row_new;
+    t.vcol_new = col_new;
+    t.numel = rows * cols;
+    t.rows = static_cast<int32_t>(rows);
+    t.cols = static_cast<int32_t>(cols);
+    t.kind = QF_KIND_RANK1;
+    t.dtype = dtype;
+    const bool vec = aligned(p, 16) && aligned(g, 16) && aligned(m_codes, 4) && aligned(v_codes, 4);
+    if (vec) t.flags |= qf::kFlagVec;
+    int64_t items = flat_items(t.numel), pre_items = items;
+    if (vec && cols % qf::kPanelCols == 0 && aligned(v_col, 16)) {
+        t.flags |= qf::kFlagPanel;
+        t.panels = static_cast<int32_t>(cols / qf::kPanelCols);
+        items = (rows + qf::kRowsPerItem - 1) / qf::kRowsPerItem * t.panels;
+        pre_items = (rows + qf::kPreRowsPerItem - 1) / qf::kPreRowsPerItem * t.panels;
+    }
+    const bool panel = t.flags & qf::kFlagPanel;
+
+    struct Header {
+        uint32_t status[64];
+        qf::DevTensor t;
+        int64_t base[kTables][2];
+    } h;
+    static_assert(sizeof(Header) <= kNoAllocHeader, "header must fit");
+    memset(&h, 0, sizeof h);
+    h.t = t;
+    h.base[kMainPanel][1] = panel ? items : 0;
+    h.base[kMainFlat][1] = panel ? 0 : items;
+    h.base[kPrePanel][1] = panel ? pre_items : 0;
+    h.base[kPreFlat][1] = panel ? 0 : pre_items;
+    // The header goes up from this stack frame; a copy from pageable memory returns once the source has
+    // been staged, so the frame may die afterwards.  The status word is cleared along with it.
+    QF_CUDA(cudaMemcpyAsync(scratch, &h, sizeof h, cudaMemcpyHostToDevice, st));
+
+    Plan pl;
+    pl.n = 1;
+    pl.n_rank1 = 1;
+    pl.d_status = reinterpret_cast<uint32_t*>(scratch);
+    pl.d_tensors = reinterpret_cast<qf::DevTensor*>(scratch + offsetof(Header, t));
+    for (int k = 0; k < kTables; ++k) {
+        pl.items[k] = h.base[k][1];
+        pl.d_base[k] = reinterpret_cast<int64_t*>(scratch + offsetof(Header, base)) + 2 * k;
+    }
+    qf::HyperPack hp;
+    memset(&hp, 0, sizeof hp);
+    hp.h[0] = widen_hyper(*hyper);
+    if (int rc = launch_pre(pl, hp, st)) return rc;   // clears the new maxima first: the array keeps the last call's
+    return launch_main(pl, hp, st);
 }
 
 }  // extern "C"
