@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define QF_ABI_VERSION 1
+#define QF_ABI_VERSION 2
 #define QF_BLOCK 128        /* elements per quantization block (optim/cuda_adamw_kernels.cu:431) */
 #define QF_MAX_HYPERS 16    /* hyper-parameter sets one launch can carry */
 
@@ -80,15 +80,22 @@ typedef struct QfTensorDesc {
     float* m_scale;       /* [ceil(numel/128)]; unused for QF_KIND_FP32                          */
     float* v_scale;       /* BLOCK: [ceil(numel/128)]; RANK1: row maxima [rows]; in/out          */
     float* v_col;         /* RANK1: column maxima [cols]; in/out                                 */
-    float* v_row_new;     /* RANK1: scratch [2*rows]: new row maxima, then their reciprocals     */
-    float* v_col_new;     /* RANK1: scratch [2*cols]: new column maxima, then their reciprocals  */
-    int64_t numel;
-    int64_t rows;         /* RANK1 only; rows * cols == numel                                    */
+    float* v_row_new;     /* RANK1: scratch for the new row maxima: [2*rows] if v_row_rcp is null
+                             (maxima, then their reciprocals), else [rows]                         */
+    float* v_col_new;     /* RANK1: the same for the columns: [2*cols], or [cols] with v_col_rcp  */
+    float* v_row_rcp;     /* RANK1, optional: separate scratch [rows] for the reciprocals          */
+    float* v_col_rcp;     /* RANK1, optional: separate scratch [cols] for the reciprocals          */
+    int64_t numel;        /* elements this record covers                                         */
+    int64_t rows;         /* RANK1 only; rows * cols == numel unless the record is partial       */
     int64_t cols;
+    int64_t flat_offset;  /* RANK1, partial records: elements of the rows x cols matrix that precede
+                             the first element of this record; the row/column buffers then describe
+                             the whole matrix while p, g, m, v, m_scale start at this record      */
     int32_t kind;         /* QfKind                                                              */
     int32_t dtype;        /* QfDtype of p and g                                                  */
     int32_t hyper;        /* index into the hyper-parameter array of the call                    */
-    int32_t reserved;
+    int32_t partial;      /* RANK1: non-zero if the record covers only part of the matrix (a shard);
+                             flat_offset and numel must be multiples of 128 except at the matrix end */
 } QfTensorDesc;
 
 int qf_abi_version(void);

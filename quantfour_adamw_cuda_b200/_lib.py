@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 # QUANTFOUR_B200_LIB may name another build of the same library (e.g. one compiled with different tuning macros).
 LIB_PATH = os.environ.get("QUANTFOUR_B200_LIB") or os.path.join(HERE, "libquantfour_b200.so")
 
-QF_ABI_VERSION = 1
+QF_ABI_VERSION = 2
 QF_MAX_HYPERS = 16
 QF_F32, QF_BF16 = 0, 1
 QF_KIND_FP32, QF_KIND_BLOCK, QF_KIND_RANK1 = 0, 1, 2
@@ -28,13 +28,13 @@ class QfTensorDesc(C.Structure):
     _fields_ = [
         ("p", C.c_void_p), ("g", C.c_void_p), ("m", C.c_void_p), ("v", C.c_void_p),
         ("m_scale", C.c_void_p), ("v_scale", C.c_void_p), ("v_col", C.c_void_p),
-        ("v_row_new", C.c_void_p), ("v_col_new", C.c_void_p),
-        ("numel", C.c_int64), ("rows", C.c_int64), ("cols", C.c_int64),
-        ("kind", C.c_int32), ("dtype", C.c_int32), ("hyper", C.c_int32), ("reserved", C.c_int32),
+        ("v_row_new", C.c_void_p), ("v_col_new", C.c_void_p), ("v_row_rcp", C.c_void_p), ("v_col_rcp", C.c_void_p),
+        ("numel", C.c_int64), ("rows", C.c_int64), ("cols", C.c_int64), ("flat_offset", C.c_int64),
+        ("kind", C.c_int32), ("dtype", C.c_int32), ("hyper", C.c_int32), ("partial", C.c_int32),
     ]
 
 
-assert C.sizeof(QfTensorDesc) == 112 and C.sizeof(QfHyper) == 32
+assert C.sizeof(QfTensorDesc) == 136 and C.sizeof(QfHyper) == 32
 
 _STEP_ARGS = [C.POINTER(QfTensorDesc), C.c_int, C.POINTER(QfHyper), C.c_int, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]
 _SCALARS = [C.c_double] * 6

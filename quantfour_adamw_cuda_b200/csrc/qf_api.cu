@@ -115,9 +115,10 @@ int build_plan(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* wor
         }
         int64_t items = flat_items(d.numel), pre_items = items;
         if (d.kind == QF_KIND_RANK1) {
-            if (d.rows <= 0 || d.cols <= 0 || d.rows * d.cols != d.numel || d.rows > INT32_MAX || d.cols > INT32_MAX)
-                return fail(QF_ERR_BAD_ARG, "tensor %d: rows*cols must equal numel (rows=%lld cols=%lld numel=%lld)", i,
-                            (long long)d.rows, (long long)d.cols, (long long)d.numel);
+            if (d.rows <= 0 || d.cols <= 0 || d.rows > INT32_MAX || d.cols > INT32_MAX || d.flat_offset < 0 ||
+                d.flat_offset + d.numel > d.rows * d.cols || (d.flat_offset == 0 && !d.partial && d.rows * d.cols != d.numel))
+                return fail(QF_ERR_BAD_ARG, "tensor %d: rows*cols must equal numel, or the record must be marked partial and lie inside the matrix (rows=%lld cols=%lld numel=%lld offset=%lld)",
+                            i, (long long)d.rows, (long long)d.cols, (long long)d.numel, (long long)d.flat_offset);
             if (!d.v_col || !d.v_row_new || !d.v_col_new) return fail(QF_ERR_BAD_ARG, "tensor %d: null rank-1 buffer", i);
             if (!aligned(d.v_col, 4) || !aligned(d.v_row_new, 4) || !aligned(d.v_col_new, 4))
                 return fail(QF_ERR_BAD_ARG, "tensor %d: rank-1 buffers misaligned", i);
@@ -126,7 +127,13 @@ int build_plan(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* wor
             t.vcol = d.v_col;
             t.vrow_new = d.v_row_new;
             t.vcol_new = d.v_col_new;
-            const bool panel = vec && d.cols % qf::kPanelCols == 0 && aligned(d.v_col, 16) && aligned(d.v_col_new, 16);
+            t.vrow_rcp = d.v_row_rcp ? d.v_row_rcp : d.v_row_new + d.rows;
+            t.vcol_rcp = d.v_col_rcp ? d.v_col_rcp : d.v_col_new + d.cols;
+            t.flat_off = d.flat_offset;
+            if (!aligned(t.vrow_rcp, 4) || !aligned(t.vcol_rcp, 4)) return fail(QF_ERR_BAD_ARG, "tensor %d: rank-1 buffers misaligned", i);
+            const bool whole = d.flat_offset == 0 && d.rows * d.cols == d.numel;
+            const bool panel = whole && vec && d.cols % qf::kPanelCols == 0 && aligned(d.v_col, 16) && aligned(d.v_col_new, 16) &&
+                               aligned(t.vcol_rcp, 16);
             if (panel) {
                 t.flags |= qf::kFlagPanel;
                 t.panels = static_cast<int32_t>(d.cols / qf::kPanelCols);
@@ -516,6 +523,8 @@ int qf_step_rank1_noalloc(void* p, const void* g, void* m_codes, void* v_codes, 
     t.vcol = v_col;
     t.vrow_new = row_new;
     t.vcol_new = col_new;
+    t.vrow_rcp = row_new + rows;
+    t.vcol_rcp = col_new + cols;
     t.numel = rows * cols;
     t.rows = static_cast<int32_t>(rows);
     t.cols = static_cast<int32_t>(cols);

@@ -41,17 +41,20 @@ struct DevTensor {
     float* ms;
     float* vs;        // BLOCK: block scales; RANK1: row maxima
     float* vcol;
-    float* vrow_new;  // [2*rows]: new row maxima, then their reciprocals
-    float* vcol_new;  // [2*cols]: new column maxima, then their reciprocals
-    int64_t numel;
+    float* vrow_new;  // [rows]: new row maxima
+    float* vcol_new;  // [cols]: new column maxima
+    float* vrow_rcp;  // [rows]: reciprocals of the new row maxima (NaN-tagged, see rank1_roll_kernel)
+    float* vcol_rcp;  // [cols]: the same for the columns
+    int64_t numel;    // elements this record covers
+    int64_t flat_off; // RANK1, flat mapping: elements of the matrix that precede this record's first one
     int32_t rows, cols;
     int32_t kind, dtype, hyper;
     int32_t flags;    // kFlagVec | kFlagPanel
     int32_t panels;   // panels per row band (cols / 256) for the panel mapping
     int32_t pad0;
-    int64_t pad1[2];
+    int64_t pad1[3];
 };
-static_assert(sizeof(DevTensor) == 128, "DevTensor must stay 128 bytes");
+static_assert(sizeof(DevTensor) == 160, "DevTensor must stay 160 bytes");
 
 constexpr int kFlagVec = 1;    // every buffer is aligned for the vector path
 constexpr int kFlagPanel = 2;  // rank-1 tensor uses the panel mapping
@@ -448,7 +451,7 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
         float col_old[8], col_new[8], rcol[8];
         load8f(t.vcol, j0, col_old);
         load8f(t.vcol_new, j0, col_new);
-        load8f(t.vcol_new + t.cols, j0, rcol);
+        load8f(t.vcol_rcp, j0, rcol);
 #pragma unroll
         for (int k = 0; k < 8; ++k) ok &= rcol[k] == rcol[k] && col_old[k] > 0.0f;
 #pragma unroll
@@ -470,7 +473,7 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
         o.ms_old = __ldg(t.ms + (e >> 7));
         o.row_old = __ldg(t.vs + r);
         o.row_new = __ldcg(t.vrow_new + r);
-        o.rrow = __ldcg(t.vrow_new + t.rows + r);
+        o.rrow = __ldcg(t.vrow_rcp + r);
         return o;
     };
     RowScalars sc_next = fetch_scalars(r0);
@@ -595,7 +598,7 @@ __device__ __forceinline__ void pre_flat_rank1(const DevTensor& t, int64_t li, c
         int ri[8], ci[8];
         load8_masked<T>(t.g, e, nv, vec, g);
         const uint32_t wv = load_codes(vc, e, nv, vec);
-        rank1_scales(t.vs, t.vcol, e, nv, t.cols, sc, ri, ci);
+        rank1_scales(t.vs, t.vcol, e + t.flat_off, nv, t.cols, sc, ri, ci);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             if (k < nv) {
@@ -645,8 +648,8 @@ __device__ __noinline__ void main_flat_run_exact(const DevTensor* tp, int64_t wb
 #pragma unroll
         for (int k = 0; k < 8; ++k) sc_old[k] = sc_new[k] = 0.0f;
         if (nv) {
-            rank1_scales(t.vs, t.vcol, e, nv, t.cols, sc_old, ri, ci);
-            rank1_scales(t.vrow_new, t.vcol_new, e, nv, t.cols, sc_new, ri, ci);
+            rank1_scales(t.vs, t.vcol, e + t.flat_off, nv, t.cols, sc_old, ri, ci);
+            rank1_scales(t.vrow_new, t.vcol_new, e + t.flat_off, nv, t.cols, sc_new, ri, ci);
         }
     }
 #pragma unroll
@@ -869,13 +872,13 @@ rank1_roll_kernel(const DevTensor* __restrict__ tensors, int n, int mode) {
         const bool is_row = i < t.rows;
         const int k = is_row ? i : i - t.rows;
         float* nw = is_row ? t.vrow_new : t.vcol_new;
-        const int len = is_row ? t.rows : t.cols;
+        float* rcp = is_row ? t.vrow_rcp : t.vcol_rcp;
         if (mode == kRollClear) {
             nw[k] = 0.0f;
         } else if (mode == kRollRecip) {
             const float x = nw[k], old = (is_row ? t.vs : t.vcol)[k];
             const float r = x == 0.0f ? 0.0f : __frcp_rn(x);
-            nw[len + k] = scale_safe(x) && scale_safe(old) ? r : __uint_as_float(0x7fc00000u);
+            rcp[k] = scale_safe(x) && scale_safe(old) ? r : __uint_as_float(0x7fc00000u);
         } else {
             (is_row ? t.vs : t.vcol)[k] = nw[k];
         }

@@ -1,0 +1,388 @@
+"""ShardedFourBitAdamW: the 4-bit AdamW step with the optimizer state sharded over data-parallel ranks.
+
+The reference has no sharding or collectives (its only distributed call is an unused seed broadcast,
+optim/adamw_fourbit_triton.py:163-165); this module adds the one place where the path shards naturally.
+
+Layout.  All parameters (in optimizer order) are laid out in one flat buffer; every tensor starts at a
+multiple of 128 elements so that its 128-element quantization blocks coincide with blocks of the flat
+space.  The flat space is cut into `world` equal ranges of `shard` elements (a multiple of 128).  Rank r
+owns the optimizer state of range r and updates the parameters in it; parameters and gradients stay
+replicated.  After the step each rank's range is all-gathered in place into every rank's flat buffer.
+
+A 2-D tensor cut by a range boundary keeps its rank-1 second-moment scales identical to the unsharded
+optimizer: the new row / column maxima of such a tensor are combined with an element-wise max over the
+ranks (one small all-reduce between the two halves of the step, qf_step_pre and qf_step_main).  Inside
+one rank a cut tensor becomes up to three records: a partial first row, whole rows (fast panel mapping),
+a partial last row.
+
+The arithmetic runs in a backend: `CudaBackend` (the C ABI) is the only one shipped; it refuses CPU
+tensors.  Tests inject a CPU backend to exercise partitioning, exchange and collectives with gloo.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .optimizer import BLOCK, DEFAULT_THRESHOLD, make_hyper
+
+__all__ = ["ShardedFourBitAdamW", "FlatLayout", "flat_layout", "rank_records", "Record", "CudaBackend"]
+
+FP32, BLOCKQ, RANK1 = _lib.QF_KIND_FP32, _lib.QF_KIND_BLOCK, _lib.QF_KIND_RANK1
+
+
+def _round_up(x: int, a: int) -> int:
+    return (x + a - 1) // a * a
+
+
+@dataclass
+class FlatLayout:
+    shapes: List[Tuple[int, ...]]
+    numels: List[int]
+    offsets: List[int]   # start of each tensor in the flat space (multiples of 128)
+    world: int
+    shard: int           # elements per rank (multiple of 128)
+
+    @property
+    def total(self) -> int:
+        return self.world * self.shard
+
+    def range_of(self, rank: int) -> Tuple[int, int]:
+        return rank * self.shard, (rank + 1) * self.shard
+
+    def owners(self, t: int) -> List[int]:
+        """Ranks whose range intersects tensor t."""
+        lo, hi = self.offsets[t], self.offsets[t] + self.numels[t]
+        return [r for r in range(self.world) if r * self.shard < hi and (r + 1) * self.shard > lo]
+
+
+def flat_layout(shapes: Sequence[Sequence[int]], world: int) -> FlatLayout:
+    shapes = [tuple(int(d) for d in s) for s in shapes]
+    numels = [math.prod(s) if s else 1 for s in shapes]
+    offsets, pos = [], 0
+    for n in numels:
+        offsets.append(pos)
+        pos = _round_up(pos + n, BLOCK)
+    shard = _round_up(-(-max(pos, 1) // world), BLOCK)
+    return FlatLayout(shapes, numels, offsets, world, shard)
+
+
+@dataclass
+class Record:
+    """One unit of work of a rank: a contiguous piece [a, b) of tensor `tensor` (tensor-relative elements)."""
+    tensor: int
+    kind: int
+    a: int
+    b: int
+    rows: int = 0          # RANK1: rows / cols of what the row / column buffers of this record describe
+    cols: int = 0
+    row_lo: int = 0        # RANK1 whole-row records: first row of the piece inside the tensor
+    flat_offset: int = 0   # RANK1 partial records: elements of the matrix before the piece
+    partial: bool = False
+
+    @property
+    def numel(self) -> int:
+        return self.b - self.a
+
+
+def tensor_kind(shape: Tuple[int, ...], numel: int, threshold: int) -> int:
+    if threshold and numel <= threshold:
+        return FP32
+    return RANK1 if len(shape) == 2 else BLOCKQ
+
+
+def rank_records(layout: FlatLayout, rank: int, threshold: int = DEFAULT_THRESHOLD) -> List[Record]:
+    lo, hi = layout.range_of(rank)
+    out: List[Record] = []
+    for t, (shape, n, off) in enumerate(zip(layout.shapes, layout.numels, layout.offsets)):
+        a, b = max(lo, off) - off, min(hi, off + n) - off
+        if a >= b:
+            continue
+        kind = tensor_kind(shape, n, threshold)
+        if kind != RANK1:
+            out.append(Record(t, kind, a, b))
+            continue
+        R, Cc = shape
+        if a == 0 and b == n:
+            out.append(Record(t, RANK1, 0, n, rows=R, cols=Cc))
+            continue
+        r_lo, r_hi = -(-a // Cc), b // Cc       # whole rows inside [a, b)
+        if Cc % BLOCK or r_lo >= r_hi:
+            # blocks straddle rows, or less than one whole row: one partial record
+            out.append(Record(t, RANK1, a, b, rows=R, cols=Cc, flat_offset=a, partial=True))
+            continue
+        if a < r_lo * Cc:
+            out.append(Record(t, RANK1, a, r_lo * Cc, rows=R, cols=Cc, flat_offset=a, partial=True))
+        out.append(Record(t, RANK1, r_lo * Cc, r_hi * Cc, rows=r_hi - r_lo, cols=Cc, row_lo=r_lo))
+        if r_hi * Cc < b:
+            out.append(Record(t, RANK1, r_hi * Cc, b, rows=R, cols=Cc, flat_offset=r_hi * Cc, partial=True))
+    return out
+
+
+@dataclass
+class RecordState:
+    """Tensors of one record on its owner rank (views where they alias per-tensor buffers)."""
+    rec: Record
+    p: torch.Tensor                         # flat view of the parameters of the piece
+    m: torch.Tensor                         # int8 codes or fp32 values
+    v: torch.Tensor
+    m_scale: Optional[torch.Tensor] = None
+    v_scale: Optional[torch.Tensor] = None  # BLOCK: block scales; RANK1: old row maxima as this record sees them
+    v_col: Optional[torch.Tensor] = None
+    row_new: Optional[torch.Tensor] = None
+    col_new: Optional[torch.Tensor] = None
+    row_rcp: Optional[torch.Tensor] = None
+    col_rcp: Optional[torch.Tensor] = None
+    g: Optional[torch.Tensor] = None        # set per step: flat view of the gradient of the piece
+
+
+class CudaBackend:
+    """Runs the two halves of the step through libquantfour_b200.so."""
+
+    def __init__(self) -> None:
+        self.L = _lib.lib()
+        self.sig = None
+        self.descs = None
+        self.ws: Optional[torch.Tensor] = None
+
+    def _prepare(self, states: List[RecordState]) -> None:
+        sig = tuple((s.p.data_ptr(), s.g.data_ptr(), s.m.data_ptr()) for s in states)
+        if sig == self.sig:
+            return
+        dev = states[0].p.device
+        if dev.type != "cuda":
+            raise RuntimeError("ShardedFourBitAdamW needs CUDA parameters; there is no CPU path")
+        dtype = _lib.QF_BF16 if states[0].p.dtype == torch.bfloat16 else _lib.QF_F32
+        descs = (_lib.QfTensorDesc * len(states))()
+        for d, s in zip(descs, states):
+            r = s.rec
+            d.p, d.g, d.m, d.v = s.p.data_ptr(), s.g.data_ptr(), s.m.data_ptr(), s.v.data_ptr()
+            d.numel, d.kind, d.dtype, d.hyper = r.numel, r.kind, dtype, 0
+            if r.kind == FP32:
+                continue
+            d.m_scale, d.v_scale = s.m_scale.data_ptr(), s.v_scale.data_ptr()
+            if r.kind == RANK1:
+                d.rows, d.cols, d.flat_offset, d.partial = r.rows, r.cols, r.flat_offset, int(r.partial)
+                d.v_col = s.v_col.data_ptr()
+                d.v_row_new, d.v_col_new = s.row_new.data_ptr(), s.col_new.data_ptr()
+                d.v_row_rcp, d.v_col_rcp = s.row_rcp.data_ptr(), s.col_rcp.data_ptr()
+        need = self.L.qf_workspace_bytes(len(states))
+        if self.ws is None or self.ws.numel() < need:
+            self.ws = torch.zeros(need, dtype=torch.uint8, device=dev)
+        self.descs, self.sig = descs, sig
+
+    def _call(self, fn, states: List[RecordState], hyper: _lib.QfHyper) -> None:
+        if not states:
+            return
+        self._prepare(states)
+        dev = states[0].p.device
+        harr = (_lib.QfHyper * 1)(hyper)
+        _lib.check(fn(self.descs, len(self.descs), harr, 1, self.ws.data_ptr(), self.ws.numel(), dev.index,
+                      C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)), "sharded step")
+
+    def pre(self, states: List[RecordState], hyper: _lib.QfHyper) -> None:
+        self._call(self.L.qf_step_pre, states, hyper)
+
+    def main(self, states: List[RecordState], hyper: _lib.QfHyper) -> None:
+        self._call(self.L.qf_step_main, states, hyper)
+
+
+class ShardedFourBitAdamW(torch.optim.Optimizer):
+    """FourBitAdamW with ZeRO-1 style sharding of the 4-bit state over the ranks of `process_group`.
+
+    Same constructor arguments as FourBitAdamW.  All parameters must share one dtype (float32 or bfloat16)
+    and one device, and every parameter must have a gradient at each step.  With `flatten=True` (default)
+    the parameters are moved into one flat buffer and become views of it.
+    """
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, *, fused: Optional[bool] = False,
+                 quant_threshold: int = DEFAULT_THRESHOLD, process_group=None, backend=None,
+                 rank: Optional[int] = None, world: Optional[int] = None):
+        if not 0.0 < lr:
+            raise ValueError(f"Invalid learning rate: {lr=}")
+        if not 0.0 < eps:
+            raise ValueError(f"Invalid eps value: {eps=}")
+        if not 0.0 < betas[0] < 1.0:
+            raise ValueError(f"Invalid Beta[0]: {betas[0]=}")
+        if not 0.0 < betas[1] < 1.0:
+            raise ValueError(f"Invalid Beta[1]: {betas[1]=}")
+        if not 0.0 <= weight_decay:
+            raise ValueError(f"Invalid weight_decay value: {weight_decay=}")
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, fused=fused))
+        if len(self.param_groups) != 1:
+            raise ValueError("ShardedFourBitAdamW takes one parameter group")
+        self.param_quant_threshold = int(quant_threshold)
+        self.group = process_group
+        self.sharded = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(process_group) if self.sharded else 1
+        self.rank = dist.get_rank(process_group) if self.sharded else 0
+        if world is not None:
+            # explicit placement without a process group: the caller moves the maxima and the parameter
+            # ranges between the instances itself (step_pre / step_main); used to run several ranks in one process
+            self.sharded, self.world, self.rank = False, int(world), int(rank or 0)
+        self.backend = backend if backend is not None else CudaBackend()
+        self.params: List[torch.Tensor] = list(self.param_groups[0]["params"])
+        p0 = self.params[0]
+        if any(p.dtype != p0.dtype or p.device != p0.device for p in self.params):
+            raise ValueError("all parameters must share dtype and device")
+        if p0.dtype not in (torch.float32, torch.bfloat16):
+            raise TypeError(f"parameters must be float32 or bfloat16, got {p0.dtype}")
+        self.layout = flat_layout([p.shape for p in self.params], self.world)
+        self.step_count = 0
+        self._flatten()
+        self._build_state()
+
+    # ---- set-up -----------------------------------------------------------------------------------
+
+    def _flatten(self) -> None:
+        p0 = self.params[0]
+        self.flat = torch.zeros(self.layout.total, dtype=p0.dtype, device=p0.device)
+        with torch.no_grad():
+            for p, off, n in zip(self.params, self.layout.offsets, self.layout.numels):
+                view = self.flat[off:off + n].view(p.shape)
+                view.copy_(p)
+                p.data = view
+
+    def _build_state(self) -> None:
+        dev = self.flat.device
+        lay = self.layout
+        self.records = rank_records(lay, self.rank, self.param_quant_threshold)
+        # tensors cut by a range boundary: every rank keeps their full row/column buffers in one shared
+        # allocation (same layout on all ranks) so that one all-reduce combines the new maxima
+        self.split = [t for t in range(len(self.params))
+                      if tensor_kind(lay.shapes[t], lay.numels[t], self.param_quant_threshold) == RANK1 and len(lay.owners(t)) > 1]
+        f32 = dict(dtype=torch.float32, device=dev)
+        # a tensor's buffer is [rows padded to a multiple of 4 | cols padded likewise]: keeps the column part
+        # 16-byte aligned for the vector path
+        def buf_len(t):
+            return _round_up(lay.shapes[t][0], 4) + _round_up(lay.shapes[t][1], 4)
+        sizes = {t: buf_len(t) for t in self.split}
+        self.shared_new = torch.zeros(sum(sizes.values()), **f32)
+        self.shared_pos, pos = {}, 0
+        for t in self.split:
+            self.shared_pos[t] = pos
+            pos += sizes[t]
+        # per-tensor rank-1 buffers: (old, new, rcp), each [R + C]; `new` of a split tensor aliases shared_new
+        self.rank1_buf: Dict[int, Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}
+        self.states: List[RecordState] = []
+        for rec in self.records:
+            t, n = rec.tensor, rec.numel
+            off = lay.offsets[t] + rec.a
+            st = RecordState(rec, self.flat[off:off + n], None, None)
+            if rec.kind == FP32:
+                st.m, st.v = torch.zeros(n, **f32), torch.zeros(n, **f32)
+            else:
+                nb, nblk = (n + 1) // 2, (n + BLOCK - 1) // BLOCK
+                st.m = torch.zeros(nb, dtype=torch.int8, device=dev)
+                st.v = torch.zeros(nb, dtype=torch.int8, device=dev)
+                st.m_scale = torch.zeros(nblk, **f32)
+                if rec.kind == BLOCKQ:
+                    st.v_scale = torch.zeros(nblk, **f32)
+                else:
+                    R, Cc = lay.shapes[t]
+                    Rp = _round_up(R, 4)
+                    if t not in self.rank1_buf:
+                        new = (self.shared_new[self.shared_pos[t]:self.shared_pos[t] + buf_len(t)] if t in self.shared_pos
+                               else torch.zeros(buf_len(t), **f32))
+                        self.rank1_buf[t] = (torch.zeros(buf_len(t), **f32), new, torch.zeros(buf_len(t), **f32))
+                    old, new, rcp = self.rank1_buf[t]
+                    r0, r1 = (rec.row_lo, rec.row_lo + rec.rows) if not rec.partial else (0, R)
+                    st.v_scale, st.row_new, st.row_rcp = old[r0:r1], new[r0:r1], rcp[r0:r1]
+                    st.v_col, st.col_new, st.col_rcp = old[Rp:Rp + Cc], new[Rp:Rp + Cc], rcp[Rp:Rp + Cc]
+            self.states.append(st)
+
+    # ---- step -------------------------------------------------------------------------------------
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        self.step_pre()
+        if self.sharded and self.world > 1 and self.shared_new.numel():
+            # element-wise max of the new row / column maxima of the tensors that are cut between ranks
+            dist.all_reduce(self.shared_new, op=dist.ReduceOp.MAX, group=self.group)
+        self.step_main()
+        if self.sharded and self.world > 1:
+            self._all_gather()
+        return loss
+
+    @torch.no_grad()
+    def step_pre(self) -> None:
+        """First half of a step: new row / column maxima of this rank's pieces (into `shared_new` for the
+        tensors that are cut between ranks)."""
+        group = self.param_groups[0]
+        flat_grads: List[torch.Tensor] = []
+        for p in self.params:
+            if p.grad is None:
+                raise RuntimeError("ShardedFourBitAdamW needs a gradient for every parameter at every step")
+            if p.grad.is_sparse:
+                raise RuntimeError("QuantFour AdamW does not support sparse gradients")
+            g = p.grad if p.grad.is_contiguous() else p.grad.contiguous()
+            if g.dtype != p.dtype:
+                raise RuntimeError("grad must match the parameter in dtype")
+            flat_grads.append(g.reshape(-1))
+        for st in self.states:
+            st.g = flat_grads[st.rec.tensor][st.rec.a:st.rec.b]
+        self.step_count += 1
+        beta1, beta2 = group["betas"]
+        self._hyper = make_hyper(group["lr"], beta1, beta2, group["eps"], group["weight_decay"], float(self.step_count))
+        if self.shared_new.numel():
+            self.shared_new.zero_()
+        self.backend.pre(self.states, self._hyper)
+
+    @torch.no_grad()
+    def step_main(self) -> None:
+        """Second half of a step: update and requantize this rank's pieces (after the maxima were combined)."""
+        self.backend.main(self.states, self._hyper)
+
+    def _all_gather(self) -> None:
+        """Every rank's range of the flat parameter buffer to every rank, in place."""
+        lo, hi = self.layout.range_of(self.rank)
+        if self.flat.is_cuda:
+            dist.all_gather_into_tensor(self.flat, self.flat[lo:hi], group=self.group)
+        else:  # CPU process groups (tests): list form, the input must not alias the outputs
+            chunks = [self.flat[r * self.layout.shard:(r + 1) * self.layout.shard] for r in range(self.world)]
+            dist.all_gather(chunks, self.flat[lo:hi].clone(), group=self.group)
+
+    # ---- checkpoint ---------------------------------------------------------------------------------
+
+    def state_dict(self) -> Dict[str, Any]:
+        """This rank's shard: its records with their state tensors, plus the layout they belong to."""
+        recs = []
+        for st in self.states:
+            r = st.rec
+            entry = {"tensor": r.tensor, "kind": r.kind, "a": r.a, "b": r.b, "exp_avg": st.m, "exp_avg_sq": st.v}
+            if r.kind != FP32:
+                entry["max1"] = st.m_scale
+            if r.kind == BLOCKQ:
+                entry["sq_max1"] = st.v_scale
+            recs.append(entry)
+        rank1 = {t: old for t, (old, _, _) in self.rank1_buf.items()}
+        return {"step": self.step_count, "rank": self.rank, "world": self.world, "shard": self.layout.shard,
+                "shapes": self.layout.shapes, "records": recs, "rank1_maxima": rank1,
+                "param_groups": [{k: v for k, v in self.param_groups[0].items() if k != "params"}]}
+
+    def load_state_dict(self, sd: Dict[str, Any]) -> None:
+        if sd["world"] != self.world or sd["rank"] != self.rank or list(map(tuple, sd["shapes"])) != self.layout.shapes:
+            raise ValueError("sharded state was written for a different world size, rank or parameter list")
+        self.step_count = int(sd["step"])
+        self.param_groups[0].update(sd["param_groups"][0])
+        by_key = {(e["tensor"], e["a"], e["b"]): e for e in sd["records"]}
+        with torch.no_grad():
+            for st in self.states:
+                e = by_key[(st.rec.tensor, st.rec.a, st.rec.b)]
+                st.m.copy_(e["exp_avg"])
+                st.v.copy_(e["exp_avg_sq"])
+                if st.rec.kind != FP32:
+                    st.m_scale.copy_(e["max1"])
+                if st.rec.kind == BLOCKQ:
+                    st.v_scale.copy_(e["sq_max1"])
+            for t, old in sd["rank1_maxima"].items():
+                self.rank1_buf[t][0].copy_(old)

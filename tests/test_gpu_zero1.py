@@ -1,0 +1,69 @@
+"""GPU tests of the sharded optimizer: one rank through the public class, and several ranks emulated in one
+process on one GPU (the exchange of maxima and parameter ranges done by the test), against the CPU oracle.
+The emulation exercises the partial-record kernels (pieces that start in the middle of a matrix)."""
+import pytest
+import torch
+
+from oracle import c_oracle as CO
+from oracle import torch_oracle as TO
+from quantfour_adamw_cuda_b200.zero1 import ShardedFourBitAdamW
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(300, 256), (1000,), (96, 128), (5000,), (64, 77), (40, 50), (130, 384), (4096,), (512, 512)]
+HP = (1e-3, 0.9, 0.999, 1e-8, 0.01)
+
+
+def _oracle_run(dtype, steps, seed):
+    gen = torch.Generator().manual_seed(seed)
+    params = [(torch.randn(s, generator=gen) * 0.02).to(dtype) for s in SHAPES]
+    init = [p.clone() for p in params]
+    states = [TO.TensorState.zeros(s) for s in SHAPES]
+    grads = []
+    for _ in range(steps):
+        gs = [(torch.randn(s, generator=gen) * 1e-3).to(dtype) for s in SHAPES]
+        grads.append(gs)
+        for p, g, st in zip(params, gs, states):
+            CO.step_tensor(p, g, st, *HP)
+    return init, grads, params
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_single_rank_matches_oracle(dtype):
+    init, grads, want = _oracle_run(dtype, 4, 0)
+    params = [torch.nn.Parameter(p.cuda()) for p in init]
+    opt = ShardedFourBitAdamW(params, lr=1e-3)
+    for gs in grads:
+        for p, g in zip(params, gs):
+            p.grad = g.cuda()
+        opt.step()
+    for i, (p, w) in enumerate(zip(params, want)):
+        assert torch.equal(p.detach().cpu(), w), f"tensor {i} {SHAPES[i]}"
+
+
+@pytest.mark.parametrize("world", [2, 3, 5])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_emulated_ranks_match_unsharded_oracle(world, dtype):
+    init, grads, want = _oracle_run(dtype, 4, 1)
+    ranks = []
+    for r in range(world):
+        params = [torch.nn.Parameter(p.cuda()) for p in init]
+        ranks.append((params, ShardedFourBitAdamW(params, lr=1e-3, rank=r, world=world)))
+    shard = ranks[0][1].layout.shard
+    for gs in grads:
+        for params, opt in ranks:
+            for p, g in zip(params, gs):
+                p.grad = g.cuda()
+            opt.step_pre()
+        if ranks[0][1].shared_new.numel():      # what the all-reduce(MAX) does
+            combined = torch.stack([opt.shared_new for _, opt in ranks]).max(dim=0).values
+            for _, opt in ranks:
+                opt.shared_new.copy_(combined)
+        for _, opt in ranks:
+            opt.step_main()
+        for r, (_, src) in enumerate(ranks):    # what the all-gather does
+            for _, dst in ranks:
+                dst.flat[r * shard:(r + 1) * shard].copy_(src.flat[r * shard:(r + 1) * shard])
+    for params, _ in ranks:
+        for i, (p, w) in enumerate(zip(params, want)):
+            assert torch.equal(p.detach().cpu(), w), f"tensor {i} {SHAPES[i]} differs in {(p.detach().cpu() != w).sum()} places"

@@ -31,7 +31,7 @@ def test_header_symbols_are_all_exported(lib):
 
 
 def test_struct_sizes_match_header(lib):
-    assert C.sizeof(_lib.QfTensorDesc) == 9 * 8 + 3 * 8 + 4 * 4
+    assert C.sizeof(_lib.QfTensorDesc) == 11 * 8 + 4 * 8 + 4 * 4
     assert lib.qf_workspace_bytes(0) % 256 == 0 and lib.qf_workspace_bytes(10) > lib.qf_workspace_bytes(1)
 
 
