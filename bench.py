@@ -286,8 +286,8 @@ def single_gpu(args):
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
                      "algorithmic_bytes_per_step": alg_bytes, "kernels_ms": {"pre": pre_ms, "main": main_ms},
-                     "note": "whole step (clear + pre + main + roll kernels) over algorithmic bytes"},
-        "e2e": e2e, "gpu_launches": 4 * args.steps, "clocks": clocks,
+                     "note": "whole step (clear, pre, reciprocals, main panel, main flat, commit: 6 launches) over algorithmic bytes"},
+        "e2e": e2e, "gpu_launches": 6 * args.steps, "clocks": clocks,
     }
     if not args.no_cpu:
         v, cores, dt, text = run_cpu(workload, "c", 3, 1)
