@@ -132,7 +132,7 @@ int build_plan(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* wor
             t.flat_off = d.flat_offset;
             if (!aligned(t.vrow_rcp, 4) || !aligned(t.vcol_rcp, 4)) return fail(QF_ERR_BAD_ARG, "tensor %d: rank-1 buffers misaligned", i);
             const bool whole = d.flat_offset == 0 && d.rows * d.cols == d.numel;
-            const bool panel = whole && vec && d.cols % qf::kPanelCols == 0 && aligned(d.v_col, 16) && aligned(d.v_col_new, 16) &&
+            const bool panel = whole && d.numel < (1ll << 31) && vec && d.cols % qf::kPanelCols == 0 && aligned(d.v_col, 16) && aligned(d.v_col_new, 16) &&
                                aligned(t.vcol_rcp, 16);
             if (panel) {
                 t.flags |= qf::kFlagPanel;
@@ -533,7 +533,7 @@ int qf_step_rank1_noalloc(void* p, const void* g, void* m_codes, void* v_codes, 
     const bool vec = aligned(p, 16) && aligned(g, 16) && aligned(m_codes, 4) && aligned(v_codes, 4);
     if (vec) t.flags |= qf::kFlagVec;
     int64_t items = flat_items(t.numel), pre_items = items;
-    if (vec && cols % qf::kPanelCols == 0 && aligned(v_col, 16)) {
+    if (vec && t.numel < (1ll << 31) && cols % qf::kPanelCols == 0 && aligned(v_col, 16)) {
         t.flags |= qf::kFlagPanel;
         t.panels = static_cast<int32_t>(cols / qf::kPanelCols);
         items = (rows + qf::kRowsPerItem - 1) / qf::kRowsPerItem * t.panels;

@@ -245,8 +245,8 @@ __device__ __noinline__ uint32_t quantize8_pairs_exact(f2 a, f2 b, f2 c, f2 d, f
 // First-moment codes of a lane's 8 values against the block scale; fast division when the scale allows.
 __device__ __forceinline__ uint32_t quantize_m8(const f2 (&m)[4], float scale, const Smem& s) {
     if (!scale_safe(scale)) return quantize8_pairs_exact(m[0], m[1], m[2], m[3], scale, s.t.mm);
-    const float r = scale == 0.0f ? 0.0f : __frcp_rn(scale);
-    const f2 r2 = bc2(r), ns2 = bc2(-scale);
+    const Recip rc = make_recip(scale);  // 0 for an all-zero block: every quotient is 0
+    const f2 r2 = bc2(rc.r), ns2 = bc2(rc.nd);
     uint32_t w = 0;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -402,6 +402,13 @@ __device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
                  : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// A read-only scalar load the compiler may not sink below the following cp.async.wait_group (volatile asm
+// statements keep their order): the loads for the next row have to be issued before this row's wait.
+__device__ __forceinline__ float ldg_early(const float* p) {
+    float v;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(__cvta_generic_to_global(p)));
+    return v;
+}
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
@@ -425,27 +432,33 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
     constexpr int kRowBytes = 2 * kArr + 256;
     constexpr int kStages = kRingBytes / kRowBytes;
     static_assert(kStages >= 3, "ring too small");
-    auto issue = [&](int r, int slot) {
-        if (r < r1) {
-            const int64_t e = static_cast<int64_t>(r) * t.cols + j0;
-            char* base = stage + slot * kRowBytes;
+    // Element offsets inside the tensor fit 32 bits (the host gives larger tensors the flat mapping), so a
+    // row costs one 32-bit add per running offset and one widening add per address.
+    const uint32_t cols = static_cast<uint32_t>(t.cols);
+    auto issue = [&](uint32_t e, int slot) {
+        char* base = stage + slot * kRowBytes;
 #pragma unroll
-            for (int v = 0; v < NV; ++v) {
-                cp_async16(base + (v * 32 + lane) * 16, t.p + e * sizeof(T) + v * 16);
-                cp_async16(base + kArr + (v * 32 + lane) * 16, t.g + e * sizeof(T) + v * 16);
-            }
-            cp_async4(base + 2 * kArr + lane * 4, mc + (e >> 1));
-            cp_async4(base + 2 * kArr + 128 + lane * 4, vc + (e >> 1));
+        for (int v = 0; v < NV; ++v) {
+            cp_async16(base + (v * 32 + lane) * 16, t.p + static_cast<size_t>(e) * sizeof(T) + v * 16);
+            cp_async16(base + kArr + (v * 32 + lane) * 16, t.g + static_cast<size_t>(e) * sizeof(T) + v * 16);
         }
-        cp_async_commit();  // one group per row, empty past the end, so that the group count stays in step
+        cp_async4(base + 2 * kArr + lane * 4, mc + (e >> 1));
+        cp_async4(base + 2 * kArr + 128 + lane * 4, vc + (e >> 1));
     };
+    uint32_t e_issue = static_cast<uint32_t>(r0) * cols + j0;  // next row to stage
+    int r_issue = r0;
 #pragma unroll
-    for (int i = 0; i < kStages - 1; ++i) issue(r0 + i, i);
+    for (int i = 0; i < kStages - 1; ++i) {
+        if (r_issue < r1) issue(e_issue, i);
+        cp_async_commit();  // one group per row, empty past the end, so that the group count stays in step
+        e_issue += cols;
+        ++r_issue;
+    }
 
     // The pass that stored the reciprocals wrote NaN where an old or new maximum is outside the range of
     // the fast sequences.  A zero old maximum (first step, rows never touched) lets v fall below the range
     // of the unchecked square root, so such rows and columns take the exact path as well.
-    f2* colbuf = reinterpret_cast<f2*>(stage + kRingBytes);  // [old | -new | 1/new][pair][lane]
+    f2* colbuf = reinterpret_cast<f2*>(stage + kRingBytes) + lane;  // [old | -new | 1/new][pair][lane]
     bool ok = hd.fast;
     {
         float col_old[8], col_new[8], rcol[8];
@@ -456,9 +469,9 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
         for (int k = 0; k < 8; ++k) ok &= rcol[k] == rcol[k] && col_old[k] > 0.0f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            colbuf[(0 * 4 + j) * 32 + lane] = mk2(col_old[2 * j], col_old[2 * j + 1]);
-            colbuf[(1 * 4 + j) * 32 + lane] = mk2(-col_new[2 * j], -col_new[2 * j + 1]);
-            colbuf[(2 * 4 + j) * 32 + lane] = mk2(rcol[2 * j], rcol[2 * j + 1]);
+            colbuf[(0 * 4 + j) * 32] = mk2(col_old[2 * j], col_old[2 * j + 1]);
+            colbuf[(1 * 4 + j) * 32] = mk2(-col_new[2 * j], -col_new[2 * j + 1]);
+            colbuf[(2 * 4 + j) * 32] = mk2(rcol[2 * j], rcol[2 * j + 1]);
         }
     }
     const bool col_fast = __all_sync(kFull, ok);
@@ -467,25 +480,30 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
     struct RowScalars {
         float ms_old, row_old, row_new, rrow;
     };
-    auto fetch_scalars = [&](int r) {
+    auto fetch_scalars = [&](int r, uint32_t e) {
         RowScalars o;
-        const int64_t e = static_cast<int64_t>(r) * t.cols + j0;
-        o.ms_old = __ldg(t.ms + (e >> 7));
-        o.row_old = __ldg(t.vs + r);
-        o.row_new = __ldcg(t.vrow_new + r);
-        o.rrow = __ldcg(t.vrow_rcp + r);
+        o.ms_old = ldg_early(t.ms + (e >> 7));
+        o.row_old = ldg_early(t.vs + r);
+        o.row_new = ldg_early(t.vrow_new + r);
+        o.rrow = ldg_early(t.vrow_rcp + r);
         return o;
     };
-    RowScalars sc_next = fetch_scalars(r0);
+    uint32_t e = static_cast<uint32_t>(r0) * cols + j0;
+    RowScalars sc_next = fetch_scalars(r0, e);
     int slot = 0;
-    for (int r = r0; r < r1; ++r) {
-        issue(r + kStages - 1, slot == 0 ? kStages - 1 : slot - 1);  // refill the slot the previous row used
+    for (int r = r0; r < r1; ++r, e += cols) {
+        if (r_issue < r1) issue(e_issue, slot == 0 ? kStages - 1 : slot - 1);  // refill the slot the previous row used
+        cp_async_commit();
+        e_issue += cols;
+        ++r_issue;
         const RowScalars sc = sc_next;
-        if (r + 1 < r1) sc_next = fetch_scalars(r + 1);
+        {
+            const int rn = min(r + 1, r1 - 1);  // past the end: fetch the last row again instead of branching
+            sc_next = fetch_scalars(rn, rn == r ? e : e + cols);
+        }
         cp_async_wait<kStages - 1>();  // everything but the newest kStages-1 groups has landed: row r is there
         const char* base = stage + slot * kRowBytes;
         slot = slot + 1 == kStages ? 0 : slot + 1;
-        const int64_t e = static_cast<int64_t>(r) * t.cols + j0;
         if (!(col_fast && sc.rrow == sc.rrow && sc.row_old > 0.0f)) {  // warp-uniform
             main_panel_row_exact<T>(tp, e, r, j0, hd, s, status);
             continue;
@@ -499,21 +517,20 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
         praw.widen(p);
         graw.widen(g);
         const f2 ms_old = bc2(sc.ms_old);
-        const float row_old = sc.row_old, row_new = sc.row_new, rrow = sc.rrow;
+        const float row_old = sc.row_old, nrow = -sc.row_new, rrow = sc.rrow;
         f2 m[4];
         uint32_t wq = 0;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             f2 pp = mk2(p[2 * j], p[2 * j + 1]);
             m[j] = mul2(pair_lookup(s.qm2, wm, j), ms_old);
-            const f2 co = colbuf[(0 * 4 + j) * 32 + lane], ncn = colbuf[(1 * 4 + j) * 32 + lane],
-                     rcn = colbuf[(2 * 4 + j) * 32 + lane];
+            const f2 co = colbuf[(0 * 4 + j) * 32], ncn = colbuf[(1 * 4 + j) * 32], rcn = colbuf[(2 * 4 + j) * 32];
             f2 v = mul2(pair_lookup(s.qv2, wv, j), mk2(fminf(row_old, co.x), fminf(row_old, co.y)));
             adamw_pair<true>(pp, mk2(g[2 * j], g[2 * j + 1]), m[j], v, h2);
             p[2 * j] = pp.x;
             p[2 * j + 1] = pp.y;
             // requantize v: scale = min(row', col') -> -scale = max(-row', -col'), 1/scale = max(1/row', 1/col')
-            const f2 nsv = mk2(fmaxf(-row_new, ncn.x), fmaxf(-row_new, ncn.y));
+            const f2 nsv = mk2(fmaxf(nrow, ncn.x), fmaxf(nrow, ncn.y));
             const f2 rv = mk2(fmaxf(rrow, rcn.x), fmaxf(rrow, rcn.y));
             const f2 y = fma2(div2_prepared(v, rv, nsv), bc2(16.0f), bc2(-1.5f));
             wq += code_from_y(y.x) << (8 * j);
