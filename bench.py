@@ -36,6 +36,10 @@ from quantfour_adamw_cuda_b200 import shapes as S  # noqa: E402
 
 HP = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
 FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes per algorithmic byte of a step, from one ncu capture of the two kernels on the GPT-2-medium-shaped
+# set (dram__bytes_read.sum + dram__bytes_write.sum = 3.722 GB for 2.869 GB algorithmic; the pre pass re-reads
+# gradients and second-moment codes).  Traffic grows in proportion to the elements processed.
+TRAFFIC_PER_ALGORITHMIC_BYTE = 3.722 / 2.869
 
 
 def measured_peak():
@@ -284,7 +288,9 @@ def single_gpu(args):
                    "l2": "inputs (%.1f GB per step) are far larger than L2" % (alg_bytes / 1e9),
                    "ms_per_step_min": min(per_step), "ms_per_step_max": max(per_step)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
+                     "traffic": alg_bytes * TRAFFIC_PER_ALGORITHMIC_BYTE, "traffic_note": "scaled from the ncu capture on the "
+                     "355 M-parameter set (profiles/step_main_pre_kernels_gpt2m.md)",
+                     "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
                      "algorithmic_bytes_per_step": alg_bytes, "kernels_ms": {"pre": pre_ms, "main": main_ms},
                      "note": "whole step (clear, pre, reciprocals, main panel, main flat, commit: 6 launches) over algorithmic bytes"},
         "e2e": e2e, "gpu_launches": 6 * args.steps, "clocks": clocks,
