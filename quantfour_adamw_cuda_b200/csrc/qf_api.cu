@@ -61,6 +61,7 @@ struct Plan {
     int n = 0;                    // tensors in the table (zero-size tensors dropped)
     int64_t items[kTables] = {0, 0, 0, 0};
     int n_rank1 = 0;
+    bool any_f32_panel = false;   // sizes the staging ring of the panel kernel
     qf::DevTensor* d_tensors = nullptr;
     int64_t* d_base[kTables] = {nullptr, nullptr, nullptr, nullptr};
     uint32_t* d_status = nullptr;
@@ -137,8 +138,9 @@ int build_plan(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* wor
             if (panel) {
                 t.flags |= qf::kFlagPanel;
                 t.panels = static_cast<int32_t>(d.cols / qf::kPanelCols);
-                items = (d.rows + qf::kRowsPerItem - 1) / qf::kRowsPerItem * t.panels;
+                items = (d.rows + qf::kMainRowsPerItem - 1) / qf::kMainRowsPerItem * t.panels;
                 pre_items = (d.rows + qf::kPreRowsPerItem - 1) / qf::kPreRowsPerItem * t.panels;
+                if (d.dtype == QF_F32) plan->any_f32_panel = true;
             }
             ++n_rank1;
         }
@@ -198,6 +200,27 @@ int grid_for(int64_t items, unsigned* grid) {
     return QF_OK;
 }
 
+// Grid of a multi-tensor kernel: QF_GRID_WAVES waves of CTAs (16 measured best: CTAs live long enough to amortise
+// their table set-up, yet the tail stays short), never more than there is work; warps stride over the items.
+int sm_count() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!cached[dev]) {
+        int n = 0;
+        cached[dev] = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0 ? n : 148;
+    }
+    return cached[dev];
+}
+unsigned persistent_grid(int64_t items, int per_sm) {
+    const int64_t ctas = (items + qf::kWarpsPerCta - 1) / qf::kWarpsPerCta;
+#ifndef QF_GRID_WAVES
+#define QF_GRID_WAVES 16
+#endif
+    const int64_t cap = static_cast<int64_t>(sm_count()) * per_sm * QF_GRID_WAVES;
+    return static_cast<unsigned>(ctas < cap ? ctas : cap);
+}
+
 void roll(const Plan& pl, int mode, cudaStream_t stream) {
     qf::rank1_roll_kernel<<<pl.n * qf::kRollSlices, qf::kThreads, 0, stream>>>(pl.d_tensors, pl.n, mode);
 }
@@ -205,15 +228,12 @@ void roll(const Plan& pl, int mode, cudaStream_t stream) {
 int launch_pre(const Plan& pl, const qf::HyperPack& hp, cudaStream_t stream) {
     if (pl.n_rank1 == 0) return QF_OK;
     roll(pl, qf::kRollClear, stream);
-    unsigned grid;
-    if (pl.items[kPrePanel]) {
-        if (int rc = grid_for(pl.items[kPrePanel], &grid)) return rc;
-        qf::step_pre_kernel<true><<<grid, qf::kThreads, 0, stream>>>(pl.d_tensors, pl.d_base[kPrePanel], pl.n, hp, pl.d_status);
-    }
-    if (pl.items[kPreFlat]) {
-        if (int rc = grid_for(pl.items[kPreFlat], &grid)) return rc;
-        qf::step_pre_kernel<false><<<grid, qf::kThreads, 0, stream>>>(pl.d_tensors, pl.d_base[kPreFlat], pl.n, hp, pl.d_status);
-    }
+    if (pl.items[kPrePanel])
+        qf::step_pre_kernel<true><<<persistent_grid(pl.items[kPrePanel], QF_PRE_MIN_CTAS), qf::kThreads, 0, stream>>>(
+            pl.d_tensors, pl.d_base[kPrePanel], pl.n, hp, pl.d_status);
+    if (pl.items[kPreFlat])
+        qf::step_pre_kernel<false><<<persistent_grid(pl.items[kPreFlat], QF_PRE_MIN_CTAS), qf::kThreads, 0, stream>>>(
+            pl.d_tensors, pl.d_base[kPreFlat], pl.n, hp, pl.d_status);
     QF_CUDA(cudaGetLastError());
     return QF_OK;
 }
@@ -221,17 +241,17 @@ int launch_pre(const Plan& pl, const qf::HyperPack& hp, cudaStream_t stream) {
 int launch_main(const Plan& pl, const qf::HyperPack& hp, cudaStream_t stream) {
     if (pl.n == 0) return QF_OK;
     if (pl.n_rank1) roll(pl, qf::kRollRecip, stream);
-    unsigned grid;
     if (pl.items[kMainPanel]) {
-        if (int rc = grid_for(pl.items[kMainPanel], &grid)) return rc;
-        QF_CUDA(cudaFuncSetAttribute(qf::step_main_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, qf::kMainDynSmem));
-        qf::step_main_kernel<true><<<grid, qf::kThreads, qf::kMainDynSmem, stream>>>(pl.d_tensors, pl.d_base[kMainPanel], pl.n, hp,
-                                                                                     pl.d_status);
+        const int dyn = qf::main_dyn_smem(pl.any_f32_panel);
+        const int ring = qf::kStages * (pl.any_f32_panel ? qf::kRowBytesF32 : qf::kRowBytesBf16);
+        QF_CUDA(cudaFuncSetAttribute(qf::step_main_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     qf::main_dyn_smem(true)));
+        qf::step_main_kernel<true><<<persistent_grid(pl.items[kMainPanel], QF_MAIN_MIN_CTAS), qf::kThreads, dyn, stream>>>(
+            pl.d_tensors, pl.d_base[kMainPanel], pl.n, hp, ring, pl.d_status);
     }
-    if (pl.items[kMainFlat]) {
-        if (int rc = grid_for(pl.items[kMainFlat], &grid)) return rc;
-        qf::step_main_kernel<false><<<grid, qf::kThreads, 0, stream>>>(pl.d_tensors, pl.d_base[kMainFlat], pl.n, hp, pl.d_status);
-    }
+    if (pl.items[kMainFlat])
+        qf::step_main_kernel<false><<<persistent_grid(pl.items[kMainFlat], QF_MAIN_MIN_CTAS), qf::kThreads, 0, stream>>>(
+            pl.d_tensors, pl.d_base[kMainFlat], pl.n, hp, 0, pl.d_status);
     if (pl.n_rank1) roll(pl, qf::kRollCommit, stream);
     QF_CUDA(cudaGetLastError());
     return QF_OK;
@@ -536,7 +556,7 @@ int qf_step_rank1_noalloc(void* p, const void* g, void* m_codes, void* v_codes, 
     if (vec && t.numel < (1ll << 31) && cols % qf::kPanelCols == 0 && aligned(v_col, 16)) {
         t.flags |= qf::kFlagPanel;
         t.panels = static_cast<int32_t>(cols / qf::kPanelCols);
-        items = (rows + qf::kRowsPerItem - 1) / qf::kRowsPerItem * t.panels;
+        items = (rows + qf::kMainRowsPerItem - 1) / qf::kMainRowsPerItem * t.panels;
         pre_items = (rows + qf::kPreRowsPerItem - 1) / qf::kPreRowsPerItem * t.panels;
     }
     const bool panel = t.flags & qf::kFlagPanel;
@@ -560,6 +580,7 @@ int qf_step_rank1_noalloc(void* p, const void* g, void* m_codes, void* v_codes, 
     Plan pl;
     pl.n = 1;
     pl.n_rank1 = 1;
+    pl.any_f32_panel = panel && dtype == QF_F32;
     pl.d_status = reinterpret_cast<uint32_t*>(scratch);
     pl.d_tensors = reinterpret_cast<qf::DevTensor*>(scratch + offsetof(Header, t));
     for (int k = 0; k < kTables; ++k) {

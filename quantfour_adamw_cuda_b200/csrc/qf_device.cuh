@@ -25,6 +25,8 @@ constexpr int kWarpsPerCta = 8;
 constexpr int kThreads = kWarpsPerCta * 32;
 constexpr int kPanelCols = 256;   // columns one warp covers: 32 lanes x 8 elements = two 128-blocks
 constexpr int kRowsPerItem = 16;  // rows (of kPanelCols elements) one warp work item covers
+constexpr int kMainRowsPerItem = 64;  // rows of one item of the second pass over a rank-1 panel: longer items
+                                      // amortise the per-item set-up (column maxima into shared memory)
 constexpr int kPreRowsPerItem = 64;  // the same for the first pass over a rank-1 panel: each item ends with one
                                      // red.max per column, so longer items mean fewer contended atomics
 constexpr unsigned kFull = 0xffffffffu;

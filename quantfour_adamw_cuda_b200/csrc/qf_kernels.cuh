@@ -117,6 +117,15 @@ __device__ const Lut g_mlut = make_lut();
 // Shared memory of a CTA: the 16-entry tables (exact path), the first-moment search table, and two
 // byte-indexed pair tables for the fast dequantize: a byte of packed codes (two elements) fetches the two
 // map values of either moment with one 64-bit load.
+// What the first pass needs of it.
+struct SmemPre {
+    Tables t;
+    float2 qv2[256];
+};
+__device__ __forceinline__ void load_smem(SmemPre& s) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) s.qv2[i] = make_float2(c_qv[i & 15], c_qv[i >> 4]);
+    load_tables(s.t);  // ends with __syncthreads()
+}
 struct Smem {
     Tables t;
     LutEntry mlut[2048];
@@ -271,7 +280,7 @@ __device__ __forceinline__ float absmax_pairs_to_block(const f2 (&m)[4]) {
 // =================================================================================================
 
 template <typename T>
-__device__ __forceinline__ void pre_panel(const DevTensor& t, int64_t li, const HyperDev& hd, const Smem& s,
+__device__ __forceinline__ void pre_panel(const DevTensor& t, int64_t li, const HyperDev& hd, const SmemPre& s,
                                           uint32_t* status) {
     const int lane = threadIdx.x & 31;
     const int band = static_cast<int>(li / t.panels);
@@ -288,7 +297,10 @@ __device__ __forceinline__ void pre_panel(const DevTensor& t, int64_t li, const 
     const uint8_t* vc = reinterpret_cast<const uint8_t*>(t.v);
     // Four rows per trip, all their loads issued before the first is worked on: this pass does little
     // arithmetic per byte, so it needs many bytes in flight per warp to cover HBM latency.
-    constexpr int kBatch = 4;
+#ifndef QF_PRE_BATCH
+#define QF_PRE_BATCH 4
+#endif
+    constexpr int kBatch = QF_PRE_BATCH;
     for (int rb = r0; rb < r1; rb += kBatch) {
         Raw8<T> g_raw[kBatch];
         uint32_t wvs[kBatch];
@@ -382,14 +394,18 @@ __device__ __noinline__ void main_panel_row_exact(const DevTensor* tp, int64_t e
 // Each lane copies its own 16-byte pieces of p and g and its two code words of the rows ahead into a
 // per-warp ring in shared memory with cp.async and reads them back when their row comes up.  A lane only
 // ever reads what it copied itself, so the ring needs no barrier: cp.async.wait_group orders a lane's
-// copies with its own reads.  The rows in flight per warp (4 for bf16, 2 for fp32 parameters) cover HBM
-// latency at two CTAs per SM without spending registers on it.  The per-lane column maxima (old, new,
+// copies with its own reads.  One row ahead per warp is enough at two CTAs per SM (deeper rings measured
+// slower: they take shared memory away from L1) and costs no registers.  The per-lane column maxima (old, new,
 // reciprocal of new) sit in shared memory as well and are fetched pair by pair: registers are the scarce
 // resource of this kernel.
-constexpr int kRingBytes = 3 * 32 * (2 * 2 * 16 + 8);  // per warp: 3 rows of fp32 parameters or 5 rows of bf16
+constexpr int kStages = 2;                             // this row and the next one
+constexpr int kRowBytesBf16 = 32 * (2 * 16 + 8);       // staged bytes of one row of a panel, bf16 parameters
+constexpr int kRowBytesF32 = 32 * (2 * 2 * 16 + 8);    // the same for fp32 parameters
 constexpr int kColBytes = 3 * 4 * 32 * 8;              // per warp: old / new / reciprocal column maxima of its 256 columns
-constexpr int kWarpDynSmem = kRingBytes + kColBytes;
-constexpr int kMainDynSmem = kWarpsPerCta * kWarpDynSmem;
+// Dynamic shared memory of the panel kernel: per warp a ring of kStages rows plus the column block.  The host
+// sizes the ring for fp32 rows only when the launch holds an fp32 panel tensor: less shared memory leaves more
+// L1 to the CTA, which the measurements reward.
+constexpr int main_dyn_smem(bool any_f32) { return kWarpsPerCta * (kStages * (any_f32 ? kRowBytesF32 : kRowBytesBf16) + kColBytes); }
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<unsigned>(__cvta_generic_to_shared(smem))),
@@ -416,13 +432,13 @@ __device__ __forceinline__ void cp_async_wait() {
 
 template <typename T>
 __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, const HyperDev& hd, const Smem& s,
-                                           char* stage, uint32_t* status) {
+                                           char* stage, int ring_bytes, uint32_t* status) {
     const DevTensor t = *tp;
     const int lane = threadIdx.x & 31;
     const int band = static_cast<int>(li / t.panels);
     const int panel = static_cast<int>(li - static_cast<int64_t>(band) * t.panels);
-    const int r0 = band * kRowsPerItem;
-    const int r1 = min(r0 + kRowsPerItem, t.rows);
+    const int r0 = band * kMainRowsPerItem;
+    const int r1 = min(r0 + kMainRowsPerItem, t.rows);
     const int j0 = panel * kPanelCols + lane * 8;
     uint8_t* mc = reinterpret_cast<uint8_t*>(t.m);
     uint8_t* vc = reinterpret_cast<uint8_t*>(t.v);
@@ -430,8 +446,7 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
     constexpr int NV = sizeof(T) / 2;  // 16-byte vectors per lane and array: 1 (bf16) or 2 (fp32)
     constexpr int kArr = NV * 512;     // bytes of one staged array of one row
     constexpr int kRowBytes = 2 * kArr + 256;
-    constexpr int kStages = kRingBytes / kRowBytes;
-    static_assert(kStages >= 3, "ring too small");
+    static_assert(kRowBytes == (NV == 1 ? kRowBytesBf16 : kRowBytesF32), "staged row size");
     // Element offsets inside the tensor fit 32 bits (the host gives larger tensors the flat mapping), so a
     // row costs one 32-bit add per running offset and one widening add per address.
     const uint32_t cols = static_cast<uint32_t>(t.cols);
@@ -458,7 +473,7 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
     // The pass that stored the reciprocals wrote NaN where an old or new maximum is outside the range of
     // the fast sequences.  A zero old maximum (first step, rows never touched) lets v fall below the range
     // of the unchecked square root, so such rows and columns take the exact path as well.
-    f2* colbuf = reinterpret_cast<f2*>(stage + kRingBytes) + lane;  // [old | -new | 1/new][pair][lane]
+    f2* colbuf = reinterpret_cast<f2*>(stage + ring_bytes) + lane;  // [old | -new | 1/new][pair][lane]
     bool ok = hd.fast;
     {
         float col_old[8], col_new[8], rcol[8];
@@ -599,7 +614,7 @@ __device__ __forceinline__ void rank1_scales(const float* row, const float* col,
 }
 
 template <typename T>
-__device__ __forceinline__ void pre_flat_rank1(const DevTensor& t, int64_t li, const HyperDev& hd, const Smem& s,
+__device__ __forceinline__ void pre_flat_rank1(const DevTensor& t, int64_t li, const HyperDev& hd, const SmemPre& s,
                                                uint32_t* status) {
     const int lane = threadIdx.x & 31;
     const bool vec = t.flags & kFlagVec;
@@ -789,28 +804,34 @@ __device__ __forceinline__ void main_flat(const DevTensor* tp, int64_t li, const
 // the other mapping have zero items in it.
 // =================================================================================================
 
+// The multi-tensor kernels are persistent: the host launches about as many CTAs as fit on the device and every
+// warp walks the item list with a fixed stride, so the shared-memory tables are filled once per CTA.
+#ifndef QF_PRE_MIN_CTAS
+#define QF_PRE_MIN_CTAS 3
+#endif
 template <bool PANEL>
-__global__ void __launch_bounds__(kThreads, 3)
+__global__ void __launch_bounds__(kThreads, QF_PRE_MIN_CTAS)
 step_pre_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict__ base, int n,
                 const __grid_constant__ HyperPack hp, uint32_t* status) {
-    __shared__ Smem s;
+    __shared__ SmemPre s;
     load_smem(s);
-    const int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
-    if (item >= base[n]) return;
-    const int ti = find_tensor(base, n, item);
-    const DevTensor t = tensors[ti];
-    const int64_t li = item - base[ti];
-    const HyperDev& h = hp.h[t.hyper];
-    if (PANEL) {
-        if (t.dtype == QF_BF16)
-            pre_panel<__nv_bfloat16>(t, li, h, s, status);
-        else
-            pre_panel<float>(t, li, h, s, status);
-    } else {
-        if (t.dtype == QF_BF16)
-            pre_flat_rank1<__nv_bfloat16>(t, li, h, s, status);
-        else
-            pre_flat_rank1<float>(t, li, h, s, status);
+    const int64_t total = base[n], stride = static_cast<int64_t>(gridDim.x) * kWarpsPerCta;
+    for (int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5); item < total; item += stride) {
+        const int ti = find_tensor(base, n, item);
+        const DevTensor t = tensors[ti];
+        const int64_t li = item - base[ti];
+        const HyperDev& h = hp.h[t.hyper];
+        if (PANEL) {
+            if (t.dtype == QF_BF16)
+                pre_panel<__nv_bfloat16>(t, li, h, s, status);
+            else
+                pre_panel<float>(t, li, h, s, status);
+        } else {
+            if (t.dtype == QF_BF16)
+                pre_flat_rank1<__nv_bfloat16>(t, li, h, s, status);
+            else
+                pre_flat_rank1<float>(t, li, h, s, status);
+        }
     }
 }
 
@@ -832,27 +853,28 @@ __device__ __forceinline__ void main_flat_dispatch(const DevTensor* tp, int64_t 
 template <bool PANEL>
 __global__ void __launch_bounds__(kThreads, QF_MAIN_MIN_CTAS)
 step_main_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict__ base, int n,
-                 const __grid_constant__ HyperPack hp, uint32_t* status) {
+                 const __grid_constant__ HyperPack hp, int ring_bytes, uint32_t* status) {
     __shared__ Smem s;
     load_smem(s);
-    const int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
-    if (item >= base[n]) return;
-    const int ti = find_tensor(base, n, item);
-    const DevTensor* tp = tensors + ti;
-    const int64_t li = item - base[ti];
-    const HyperDev& h = hp.h[tp->hyper];  // hp is a grid constant: its address is usable as it is
-    if (PANEL) {
-        extern __shared__ __align__(16) char staging[];  // kMainDynSmem bytes: one ring per warp
-        char* stage = staging + (threadIdx.x >> 5) * kWarpDynSmem;
-        if (tp->dtype == QF_BF16)
-            main_panel<__nv_bfloat16>(tp, li, h, s, stage, status);
-        else
-            main_panel<float>(tp, li, h, s, stage, status);
-    } else {
-        if (tp->dtype == QF_BF16)
-            main_flat_dispatch<__nv_bfloat16>(tp, li, h, s, status);
-        else
-            main_flat_dispatch<float>(tp, li, h, s, status);
+    extern __shared__ __align__(16) char staging[];  // panel kernel: per warp a ring of rows plus the column block
+    char* stage = staging + (threadIdx.x >> 5) * (ring_bytes + kColBytes);
+    const int64_t total = base[n], stride = static_cast<int64_t>(gridDim.x) * kWarpsPerCta;
+    for (int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5); item < total; item += stride) {
+        const int ti = find_tensor(base, n, item);
+        const DevTensor* tp = tensors + ti;
+        const int64_t li = item - base[ti];
+        const HyperDev& h = hp.h[tp->hyper];  // hp is a grid constant: its address is usable as it is
+        if (PANEL) {
+            if (tp->dtype == QF_BF16)
+                main_panel<__nv_bfloat16>(tp, li, h, s, stage, ring_bytes, status);
+            else
+                main_panel<float>(tp, li, h, s, stage, ring_bytes, status);
+        } else {
+            if (tp->dtype == QF_BF16)
+                main_flat_dispatch<__nv_bfloat16>(tp, li, h, s, status);
+            else
+                main_flat_dispatch<float>(tp, li, h, s, status);
+        }
     }
 }
 

@@ -104,6 +104,7 @@ class FourBitAdamW(torch.optim.Optimizer):
         super().__init__(params, defaults)
         self._scratch: Dict[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]] = {}
         self._plans: Dict[Tuple[int, int], _DevicePlan] = {}
+        self._fast: Optional[dict] = None
 
     # ---- state ---------------------------------------------------------------------------------
 
@@ -158,6 +159,7 @@ class FourBitAdamW(torch.optim.Optimizer):
         self.__dict__.setdefault("param_quant_threshold", DEFAULT_THRESHOLD)
         self._scratch = {}
         self._plans = {}
+        self._fast = None
         state_values = list(self.state.values())
         step_is_tensor = len(state_values) != 0 and torch.is_tensor(state_values[0]["step"])
         if not step_is_tensor:
@@ -192,6 +194,7 @@ class FourBitAdamW(torch.optim.Optimizer):
                 self.state[p] = place(saved, p.device)
         self._scratch = {}
         self._plans = {}
+        self._fast = None
 
     def dequantized_state(self, p: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """(exp_avg, exp_avg_sq) of ``p`` as float32 tensors shaped like ``p`` (dequantized on the GPU)."""
@@ -239,9 +242,13 @@ class FourBitAdamW(torch.optim.Optimizer):
             with torch.enable_grad():
                 loss = closure()
 
+        if self._fast is not None and self._step_fast():
+            return loss
+
         hypers: List[_lib.QfHyper] = []
         hyper_index: Dict[tuple, int] = {}
         work: Dict[torch.device, List[tuple]] = {}
+        cacheable = True
         for group in self.param_groups:
             beta1, beta2 = group["betas"]
             gkey = (group["lr"], beta1, beta2, group["eps"], group["weight_decay"])
@@ -261,6 +268,7 @@ class FourBitAdamW(torch.optim.Optimizer):
                     raise RuntimeError("grad must match the parameter in dtype, numel and device")
                 if not g.is_contiguous():
                     g = g.contiguous()
+                    cacheable = False
                 st = self.state[p]
                 if len(st) == 0:
                     self._init_state(p)
@@ -283,7 +291,67 @@ class FourBitAdamW(torch.optim.Optimizer):
                 if sel:
                     self._launch(dev, chunk, sel, hypers[lo:hi_end], lo)
                 lo, chunk = hi_end, chunk + 1
+        self._fast = None
+        if cacheable and len(work) == 1 and len(hypers) <= _lib.QF_MAX_HYPERS:
+            self._remember(next(iter(work.items())), hyper_index)
         return loss
+
+    # ---- steady state: same tensors, same gradient buffers as the step before ---------------------------
+
+    def _remember(self, dev_entries, hyper_index) -> None:
+        """Record what the step just made so that the next one can skip rebuilding it: which gradient buffers
+        were seen, which parameters had none, and the (group, step count) class behind every hyper index."""
+        dev, entries = dev_entries
+        group_of = {id(p): gi for gi, g in enumerate(self.param_groups) for p in g["params"]}
+        seen = {id(e[0]) for e in entries}
+        classes = [None] * len(hyper_index)
+        for p, _, st, hi in entries:
+            if classes[hi] is None:
+                classes[hi] = [group_of[id(p)], float(st["step"])]
+        self._fast = {
+            "dev": dev, "plan": self._plans[(dev.index, 0)], "checks": [(p, p.data_ptr(), g.data_ptr()) for p, g, _, _ in entries],
+            "absent": [p for g in self.param_groups for p in g["params"] if id(p) not in seen],
+            "steps": [st["step"] for _, _, st, _ in entries], "classes": classes,
+            "n_params": sum(len(g["params"]) for g in self.param_groups),
+        }
+
+    def _step_fast(self) -> bool:
+        f = self._fast
+        if f["n_params"] != sum(len(g["params"]) for g in self.param_groups):
+            return False
+        plan = f["plan"]
+        checks = f["checks"]
+        moved = []
+        for i, (p, pptr, gptr) in enumerate(checks):
+            g = p.grad
+            if g is None or p.data_ptr() != pptr:
+                return False
+            if g.data_ptr() != gptr:     # a new gradient buffer: only its address in the descriptor changes
+                if not g.is_contiguous() or g.dtype != p.dtype or g.numel() != p.numel() or g.is_sparse:
+                    return False
+                moved.append((i, g))
+        for p in f["absent"]:
+            if p.grad is not None:
+                return False
+        for i, g in moved:
+            plan.descs[i].g = g.data_ptr()
+            plan.keepalive[i] = g
+            checks[i] = (checks[i][0], checks[i][1], g.data_ptr())
+        if moved:
+            plan.signature = None     # the slow path must not trust its cached signature any more
+        torch._foreach_add_(f["steps"], 1.0)
+        hypers = []
+        for c in f["classes"]:
+            c[1] += 1.0
+            group = self.param_groups[c[0]]
+            beta1, beta2 = group["betas"]
+            hypers.append(make_hyper(group["lr"], beta1, beta2, group["eps"], group["weight_decay"], c[1]))
+        dev = f["dev"]
+        harr = (_lib.QfHyper * len(hypers))(*hypers)
+        rc = _lib.lib().qf_step_multi(plan.descs, len(plan.descs), harr, len(hypers), plan.workspace.data_ptr(),
+                                      plan.workspace.numel(), dev.index, C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+        _lib.check(rc, "qf_step_multi")
+        return True
 
     def _launch(self, dev: torch.device, chunk: int, entries: List[tuple], hypers: List[_lib.QfHyper], hyper_base: int) -> None:
         L = _lib.lib()
