@@ -228,12 +228,15 @@ void roll(const Plan& pl, int mode, cudaStream_t stream) {
 int launch_pre(const Plan& pl, const qf::HyperPack& hp, cudaStream_t stream) {
     if (pl.n_rank1 == 0) return QF_OK;
     roll(pl, qf::kRollClear, stream);
-    if (pl.items[kPrePanel])
-        qf::step_pre_kernel<true><<<persistent_grid(pl.items[kPrePanel], QF_PRE_MIN_CTAS), qf::kThreads, 0, stream>>>(
-            pl.d_tensors, pl.d_base[kPrePanel], pl.n, hp, pl.d_status);
+    if (pl.items[kPrePanel]) {
+        const int dyn = qf::pre_dyn_smem(pl.any_f32_panel);
+        QF_CUDA(cudaFuncSetAttribute(qf::step_pre_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, qf::pre_dyn_smem(true)));
+        qf::step_pre_kernel<true><<<persistent_grid(pl.items[kPrePanel], QF_PRE_MIN_CTAS), qf::kThreads, dyn, stream>>>(
+            pl.d_tensors, pl.d_base[kPrePanel], pl.n, hp, dyn / qf::kWarpsPerCta, pl.d_status);
+    }
     if (pl.items[kPreFlat])
         qf::step_pre_kernel<false><<<persistent_grid(pl.items[kPreFlat], QF_PRE_MIN_CTAS), qf::kThreads, 0, stream>>>(
-            pl.d_tensors, pl.d_base[kPreFlat], pl.n, hp, pl.d_status);
+            pl.d_tensors, pl.d_base[kPreFlat], pl.n, hp, 0, pl.d_status);
     QF_CUDA(cudaGetLastError());
     return QF_OK;
 }

@@ -275,79 +275,121 @@ __device__ __forceinline__ float absmax_pairs_to_block(const f2 (&m)[4]) {
     return __uint_as_float(__reduce_max_sync(mask, __float_as_uint(a)));
 }
 
+// ---- cp.async helpers (per-lane asynchronous copies global -> shared) -------------------------------------
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<unsigned>(__cvta_generic_to_shared(smem))),
+                 "l"(__cvta_generic_to_global(gmem))
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<unsigned>(__cvta_generic_to_shared(smem))),
+                 "l"(__cvta_generic_to_global(gmem))
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// A read-only scalar load the compiler may not sink below the following cp.async.wait_group (volatile asm
+// statements keep their order): the loads for the next row have to be issued before this row's wait.
+__device__ __forceinline__ float ldg_early(const float* p) {
+    float v;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(__cvta_generic_to_global(p)));
+    return v;
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // =================================================================================================
 // Panel mapping, rank-1 tensors
 // =================================================================================================
 
+// First pass over one item of a rank-1 panel.  This pass does little arithmetic per byte, so it needs many bytes in
+// flight to cover HBM latency: each lane stages its own 16-byte piece of g and its code word of the next
+// kPreStages - 1 rows into a per-warp ring with cp.async (a lane reads only what it copied, so no barrier), and the
+// old row maxima of the item are fetched up front, two per lane, and handed out by shuffle.
+constexpr int kPreStages = 8;
+constexpr int pre_dyn_smem(bool any_f32) { return kWarpsPerCta * kPreStages * 32 * ((any_f32 ? 32 : 16) + 4); }
+
 template <typename T>
 __device__ __forceinline__ void pre_panel(const DevTensor& t, int64_t li, const HyperDev& hd, const SmemPre& s,
-                                          uint32_t* status) {
+                                          char* stage, uint32_t* status) {
+    static_assert(kPreRowsPerItem == 64, "two old row maxima per lane");
     const int lane = threadIdx.x & 31;
     const int band = static_cast<int>(li / t.panels);
     const int panel = static_cast<int>(li - static_cast<int64_t>(band) * t.panels);
     const int r0 = band * kPreRowsPerItem;
     const int r1 = min(r0 + kPreRowsPerItem, t.rows);
     const int j0 = panel * kPanelCols + lane * 8;
+    const uint8_t* vc = reinterpret_cast<const uint8_t*>(t.v);
+    constexpr int NV = sizeof(T) / 2;
+    constexpr int kRowBytes = 32 * (NV * 16 + 4);
+    const uint32_t cols = static_cast<uint32_t>(t.cols);
+    auto issue = [&](uint32_t e, int slot) {
+        char* base = stage + slot * kRowBytes;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) cp_async16(base + (v * 32 + lane) * 16, t.g + static_cast<size_t>(e) * sizeof(T) + v * 16);
+        cp_async4(base + NV * 512 + lane * 4, vc + (e >> 1));
+    };
+    uint32_t e_issue = static_cast<uint32_t>(r0) * cols + j0;
+    int r_issue = r0;
+#pragma unroll
+    for (int i = 0; i < kPreStages - 1; ++i) {
+        if (r_issue < r1) issue(e_issue, i);
+        cp_async_commit();
+        e_issue += cols;
+        ++r_issue;
+    }
+    const float rows_lo = __ldg(t.vs + min(r0 + lane, r1 - 1)), rows_hi = __ldg(t.vs + min(r0 + 32 + lane, r1 - 1));
     float col_old[8];
     load8f(t.vcol, j0, col_old);
     const Hyper2 h2 = widen(hd);
     uint32_t cmax[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) cmax[k] = 0;
-    const uint8_t* vc = reinterpret_cast<const uint8_t*>(t.v);
-    // Four rows per trip, all their loads issued before the first is worked on: this pass does little
-    // arithmetic per byte, so it needs many bytes in flight per warp to cover HBM latency.
-#ifndef QF_PRE_BATCH
-#define QF_PRE_BATCH 4
-#endif
-    constexpr int kBatch = QF_PRE_BATCH;
-    for (int rb = r0; rb < r1; rb += kBatch) {
-        Raw8<T> g_raw[kBatch];
-        uint32_t wvs[kBatch];
-        float rows_old[kBatch];
+    int slot = 0;
+    for (int r = r0; r < r1; ++r) {
+        if (r_issue < r1) issue(e_issue, slot == 0 ? kPreStages - 1 : slot - 1);
+        cp_async_commit();
+        e_issue += cols;
+        ++r_issue;
+        cp_async_wait<kPreStages - 1>();
+        const char* base = stage + slot * kRowBytes;
+        slot = slot + 1 == kPreStages ? 0 : slot + 1;
+        Raw8<T> g_raw;
+        g_raw.from_shared(base, lane);
+        const uint32_t wv = *reinterpret_cast<const uint32_t*>(base + NV * 512 + lane * 4);
+        const int k_row = r - r0;
+        const float row_old = __shfl_sync(kFull, k_row < 32 ? rows_lo : rows_hi, k_row & 31);
+        float g[8];
+        g_raw.widen(g);
+        uint32_t rmax = 0;
+        if (hd.fast) {  // warp-uniform
 #pragma unroll
-        for (int i = 0; i < kBatch; ++i) {
-            const int r = min(rb + i, r1 - 1);  // past the end: reload the last row (its maxima do not change)
-            const int64_t e = static_cast<int64_t>(r) * t.cols + j0;
-            g_raw[i].load(t.g, e);
-            wvs[i] = *reinterpret_cast<const uint32_t*>(vc + (e >> 1));
-            rows_old[i] = __ldg(t.vs + r);
+            for (int j = 0; j < 4; ++j) {
+                const f2 v_old = mul2(pair_lookup(s.qv2, wv, j),
+                                      mk2(fminf(row_old, col_old[2 * j]), fminf(row_old, col_old[2 * j + 1])));
+                const f2 v = v_update2(mk2(g[2 * j], g[2 * j + 1]), v_old, h2);
+                const uint32_t b0 = __float_as_uint(v.x), b1 = __float_as_uint(v.y);  // v >= 0
+                rmax = max(rmax, max(b0, b1));
+                cmax[2 * j] = max(cmax[2 * j], b0);
+                cmax[2 * j + 1] = max(cmax[2 * j + 1], b1);
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float v_old = __fmul_rn(s.t.qv[nib(wv, k)], fminf(row_old, col_old[k]));
+                const uint32_t b = __float_as_uint(v_update(g[k], v_old, hd.h));
+                rmax = max(rmax, b);
+                cmax[k] = max(cmax[k], b);
+            }
         }
-#pragma unroll
-        for (int i = 0; i < kBatch; ++i) {
-            const int r = min(rb + i, r1 - 1);
-            const uint32_t wv = wvs[i];
-            const float row_old = rows_old[i];
-            float g[8];
-            g_raw[i].widen(g);
-            uint32_t rmax = 0;
-            if (hd.fast) {  // warp-uniform
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const f2 v_old = mul2(pair_lookup(s.qv2, wv, j),
-                                          mk2(fminf(row_old, col_old[2 * j]), fminf(row_old, col_old[2 * j + 1])));
-                    const f2 v = v_update2(mk2(g[2 * j], g[2 * j + 1]), v_old, h2);
-                    const uint32_t b0 = __float_as_uint(v.x), b1 = __float_as_uint(v.y);  // v >= 0
-                    rmax = max(rmax, max(b0, b1));
-                    cmax[2 * j] = max(cmax[2 * j], b0);
-                    cmax[2 * j + 1] = max(cmax[2 * j + 1], b1);
-                }
-            } else {
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const float v_old = __fmul_rn(s.t.qv[nib(wv, k)], fminf(row_old, col_old[k]));
-                    const uint32_t b = __float_as_uint(v_update(g[k], v_old, hd.h));
-                    rmax = max(rmax, b);
-                    cmax[k] = max(cmax[k], b);
-                }
-            }
-            rmax = __reduce_max_sync(kFull, rmax);
-            if (lane == 0) {
-                atomic_max_nonneg(t.vrow_new + r, rmax);
-                if (rmax >= 0x7f800000u) atomicOr(status, QF_STATUS_NONFINITE);
-            }
+        rmax = __reduce_max_sync(kFull, rmax);
+        if (lane == 0) {
+            atomic_max_nonneg(t.vrow_new + r, rmax);
+            if (rmax >= 0x7f800000u) atomicOr(status, QF_STATUS_NONFINITE);
         }
     }
+    cp_async_wait<0>();
 #pragma unroll
     for (int k = 0; k < 8; ++k) atomic_max_nonneg(t.vcol_new + j0 + k, cmax[k]);
 }
@@ -406,29 +448,6 @@ constexpr int kColBytes = 3 * 4 * 32 * 8;              // per warp: old / new / 
 // sizes the ring for fp32 rows only when the launch holds an fp32 panel tensor: less shared memory leaves more
 // L1 to the CTA, which the measurements reward.
 constexpr int main_dyn_smem(bool any_f32) { return kWarpsPerCta * (kStages * (any_f32 ? kRowBytesF32 : kRowBytesBf16) + kColBytes); }
-
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<unsigned>(__cvta_generic_to_shared(smem))),
-                 "l"(__cvta_generic_to_global(gmem))
-                 : "memory");
-}
-__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<unsigned>(__cvta_generic_to_shared(smem))),
-                 "l"(__cvta_generic_to_global(gmem))
-                 : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-// A read-only scalar load the compiler may not sink below the following cp.async.wait_group (volatile asm
-// statements keep their order): the loads for the next row have to be issued before this row's wait.
-__device__ __forceinline__ float ldg_early(const float* p) {
-    float v;
-    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(__cvta_generic_to_global(p)));
-    return v;
-}
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
 
 template <typename T>
 __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, const HyperDev& hd, const Smem& s,
@@ -812,9 +831,11 @@ __device__ __forceinline__ void main_flat(const DevTensor* tp, int64_t li, const
 template <bool PANEL>
 __global__ void __launch_bounds__(kThreads, QF_PRE_MIN_CTAS)
 step_pre_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict__ base, int n,
-                const __grid_constant__ HyperPack hp, uint32_t* status) {
+                const __grid_constant__ HyperPack hp, int ring_bytes, uint32_t* status) {
     __shared__ SmemPre s;
     load_smem(s);
+    extern __shared__ __align__(16) char staging[];  // panel kernel: one ring of rows per warp
+    char* stage = staging + (threadIdx.x >> 5) * ring_bytes;
     const int64_t total = base[n], stride = static_cast<int64_t>(gridDim.x) * kWarpsPerCta;
     for (int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5); item < total; item += stride) {
         const int ti = find_tensor(base, n, item);
@@ -823,9 +844,9 @@ step_pre_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict
         const HyperDev& h = hp.h[t.hyper];
         if (PANEL) {
             if (t.dtype == QF_BF16)
-                pre_panel<__nv_bfloat16>(t, li, h, s, status);
+                pre_panel<__nv_bfloat16>(t, li, h, s, stage, status);
             else
-                pre_panel<float>(t, li, h, s, status);
+                pre_panel<float>(t, li, h, s, stage, status);
         } else {
             if (t.dtype == QF_BF16)
                 pre_flat_rank1<__nv_bfloat16>(t, li, h, s, status);
