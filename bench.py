@@ -302,13 +302,56 @@ def single_gpu(args):
     print(json.dumps(out))
 
 
+def quantize_micro(args):
+    """Stand-alone quantize / dequantize micro-benchmark: first-moment path on 2^28 fp32 values ~N(0, 1e-3) with 0.1 %
+    of the entries x100 (block-128, dynamic-exponent map), second-moment path on a 16384 x 16384 fp32 matrix of squared
+    N(0, 1e-3) values (rank-1 row / column maxima).  One JSON line; GB/s over the compulsory bytes of each call."""
+    import quantfour_adamw_cuda_b200 as qf
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    n = 1 << 28
+    x = torch.randn(n, generator=torch.Generator(device=dev).manual_seed(0), device=dev) * 1e-3
+    x = torch.where(torch.rand(n, generator=torch.Generator(device=dev).manual_seed(1), device=dev) < 1e-3, x * 100, x)
+    R = C = 16384
+    v = (torch.randn(R, C, generator=torch.Generator(device=dev).manual_seed(2), device=dev) * 1e-3) ** 2
+    codes_m, sc_m = qf.quantize_m(x)
+    codes_v, row, col = qf.quantize_v(v)
+    cases = {
+        "quantize_m": (lambda: qf.quantize_m(x), n * 4.5 + n // 32),
+        "dequantize_m": (lambda: qf.dequantize_m(codes_m, sc_m, n), n * 4.5 + n // 32),
+        "quantize_v_rank1": (lambda: qf.quantize_v(v), R * C * 4.5 + 8 * R),
+        "dequantize_v_rank1": (lambda: qf.dequantize_v(codes_v, row, col), R * C * 4.5 + 8 * R),
+    }
+    peak, peak_kind = measured_peak()
+    out = {}
+    for name, (fn, nbytes) in cases.items():
+        for _ in range(max(3, args.warmup)):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(dev)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = e0.elapsed_time(e1) / args.steps
+        out[name] = {"ms": ms, "GBps": nbytes / ms / 1e6, "frac_of_peak": nbytes / ms / 1e6 / peak}
+    print(json.dumps({"metric": "stand-alone quantize / dequantize", "unit": "GB/s over compulsory bytes", "n_gpus": 1,
+                      "steps": args.steps, "data": "synthetic", "peak": peak, "peak_kind": peak_kind,
+                      "config": {"workload": "quantize", "m": "2^28 fp32", "v": "16384x16384 fp32",
+                                 "note": "the rank-1 quantize has to read its input twice (maxima, then codes): "
+                                         "a perfect implementation shows about 53 % on this scale; timings include the "
+                                         "allocation of the outputs by torch's caching allocator"},
+                      "kernels": out}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=[None, *S.WORKLOADS])
+    ap.add_argument("--workload", default=None, choices=[None, *S.WORKLOADS, "quantize"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -316,6 +359,8 @@ def main():
         return reference_arm(args)
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU arm")
+    if args.workload == "quantize":
+        return quantize_micro(args)
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         return single_gpu(args)
     from quantfour_adamw_cuda_b200 import zero1_bench

@@ -263,3 +263,83 @@ def test_unaligned_views_take_the_scalar_path():
         CO.step_tensor(p, g, st, *_hp_args())
         stepper.step([gg])
     _assert_same([p], [st], [gp], [gs])
+
+
+def _shape_list_problem(shapes, dtype, seed, sigma_seed=1234):
+    gen = torch.Generator().manual_seed(seed)
+    sig = (10 ** torch.empty(len(shapes)).uniform_(-5, -2, generator=torch.Generator().manual_seed(sigma_seed))).tolist()
+    params = [(torch.randn(s, generator=gen) * 0.02).to(dtype) for s in shapes]
+    return gen, sig, params
+
+
+def test_config3_gpt2_medium_shaped_list_single_multi_tensor_step():
+    """GPT-2-medium-shaped ragged list (292 tensors, 354.8 M parameters, bf16, per-tensor gradient sigma log-uniform in
+    [1e-5, 1e-2]): one multi-tensor step from zero state and one from warm state, every tensor against the oracle."""
+    from quantfour_adamw_cuda_b200 import shapes as S
+    shapes = S.gpt2_medium()
+    gen, sig, params = _shape_list_problem(shapes, torch.bfloat16, 7)
+    ostates = [TO.TensorState.zeros(s) for s in shapes]
+    gparams = [p.to(DEV) for p in params]
+    gstates = [GpuState(st) for st in ostates]
+    stepper = AbiStepper(gparams, gstates, **HP)
+    for step in range(3):
+        grads = [make_grad(p.shape, p.dtype, sigma=sg, gen=gen) for p, sg in zip(params, sig)]
+        for p, g, st in zip(params, grads, ostates):
+            CO.step_tensor(p, g, st, *_hp_args())
+        stepper.step([g.to(DEV) for g in grads])
+        if step in (0, 2):
+            _assert_same(params, ostates, gparams, gstates, f"step {step + 1}")
+    assert sum(st.kind == "fp32" for st in ostates) == 194 and sum(st.kind == "rank1" for st in ostates) == 98
+
+
+def test_config4_llama7b_subset_twenty_steps():
+    """Parity subset of the Llama-7B-shaped set: one decoder layer's nine tensors plus a 2048-row slice of the embedding,
+    bf16 with 0.1 % x100 outliers, 20 free-running steps (the full set has no CPU oracle run in reasonable time)."""
+    from quantfour_adamw_cuda_b200 import shapes as S
+    shapes = S.llama_7b()[1:10] + [(2048, 4096)]
+    gen, sig, params = _shape_list_problem(shapes, torch.bfloat16, 9)
+    ostates = [TO.TensorState.zeros(s) for s in shapes]
+    gparams = [p.to(DEV) for p in params]
+    gstates = [GpuState(st) for st in ostates]
+    stepper = AbiStepper(gparams, gstates, **HP)
+    for step in range(20):
+        grads = [make_grad(p.shape, p.dtype, sigma=sg, gen=gen) for p, sg in zip(params, sig)]
+        for p, g, st in zip(params, grads, ostates):
+            CO.step_tensor(p, g, st, *_hp_args())
+        stepper.step([g.to(DEV) for g in grads])
+    _assert_same(params, ostates, gparams, gstates, "after 20 steps")
+    assert stepper.status() == 0
+
+
+def test_config2_full_size_properties():
+    """Quantize / dequantize at the micro-benchmark's full sizes, checked through size-independent properties:
+    the round-trip error is bounded by half the widest gap of the map times the scale, re-quantizing the dequantized
+    second moment gives the same codes and maxima (idempotence; the first-moment map is not idempotent because its
+    lowest value is -0.8875, not -1), and the codes of a slice match the oracle on that slice."""
+    n = 1 << 28
+    g = torch.Generator(device=DEV).manual_seed(0)
+    x = torch.randn(n, generator=g, device=DEV) * 1e-3
+    mask = torch.rand(n, generator=torch.Generator(device=DEV).manual_seed(1), device=DEV) < 1e-3
+    x = torch.where(mask, x * 100, x)
+    codes, scales = qf.quantize_m(x)
+    back = qf.dequantize_m(codes, scales, n)
+    err = (back - x).abs().view(-1, 128) / scales.view(-1, 1).clamp_min(1e-30)
+    assert float(err.max()) <= 0.1126
+    sl = slice(12345 * 128, 12345 * 128 + (1 << 20))
+    oc, osc = CO.quantize_block(x[sl].cpu(), 0)
+    assert torch.equal(codes[sl.start // 2: sl.stop // 2].cpu().view(torch.uint8), oc)
+    assert torch.equal(scales[sl.start // 128: sl.stop // 128].cpu(), osc)
+    del x, back, err, mask
+    torch.cuda.empty_cache()
+    R = C = 16384
+    v = (torch.randn(R, C, generator=torch.Generator(device=DEV).manual_seed(2), device=DEV) * 1e-3) ** 2
+    codes, row, col = qf.quantize_v(v)
+    assert torch.equal(row, v.max(dim=1).values) and torch.equal(col, v.max(dim=0).values)
+    back = qf.dequantize_v(codes, row, col)
+    st = torch.min(row.view(-1, 1), col.view(1, -1))
+    assert float(((back - v).abs() / st).max()) <= 0.0625 + 1e-6
+    codes2, row2, col2 = qf.quantize_v(back)
+    assert torch.equal(row2, row) and torch.equal(col2, col) and torch.equal(codes2, codes)
+    rows = slice(5000, 5064)
+    oc = TO.pack(TO.codes_of(TO._safe_div(v[rows].cpu(), st[rows].cpu()), TO.MV))
+    assert torch.equal(codes[rows.start * C // 2: rows.stop * C // 2].cpu().view(torch.uint8), oc)
