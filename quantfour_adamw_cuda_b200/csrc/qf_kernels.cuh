@@ -1061,6 +1061,64 @@ rank1_max_kernel(const float* __restrict__ v, int rows, int cols, float* __restr
     }
 }
 
+// The same for matrices whose column count is a multiple of 256 and whose buffers are vector-aligned: panel mapping
+// (a lane keeps its 8 column maxima in registers, the row maximum is one broadcast load per row), packed division
+// and the closed-form search where the scales allow it.
+template <bool QUANT>
+__global__ void __launch_bounds__(kThreads)
+rank1_codec_panel_kernel(const float* __restrict__ in, uint8_t* __restrict__ codes, const float* __restrict__ row_max,
+                         const float* __restrict__ col_max, int rows, int cols, float* __restrict__ out) {
+    __shared__ SmemPre s;
+    load_smem(s);
+    const int lane = threadIdx.x & 31;
+    const int panels = cols / kPanelCols;
+    const int64_t total = static_cast<int64_t>((rows + kRowsPerItem - 1) / kRowsPerItem) * panels;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * kWarpsPerCta;
+    for (int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5); item < total; item += stride) {
+        const int band = static_cast<int>(item / panels);
+        const int j0 = static_cast<int>(item - static_cast<int64_t>(band) * panels) * kPanelCols + lane * 8;
+        const int r0 = band * kRowsPerItem, r1 = min(r0 + kRowsPerItem, rows);
+        float col[8];
+        load8f(col_max, j0, col);
+        bool ok = true;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ok &= scale_safe(col[k]) && col[k] > 0.0f;
+        const bool col_fast = __all_sync(kFull, ok);
+        for (int r = r0; r < r1; ++r) {
+            const int64_t e = static_cast<int64_t>(r) * cols + j0;
+            const float row = __ldg(row_max + r);
+            if (QUANT) {
+                float x[8];
+                load8f(in, e, x);
+                uint32_t w = 0;
+                if (col_fast && scale_safe(row) && row > 0.0f) {  // warp-uniform
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const f2 sc = mk2(fminf(row, col[2 * j]), fminf(row, col[2 * j + 1]));
+                        const f2 y = fma2(div2(mk2(x[2 * j], x[2 * j + 1]), sc), bc2(16.0f), bc2(-1.5f));
+                        w += code_from_y(y.x) << (8 * j);
+                        w += code_from_y(y.y) << (8 * j + 4);
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) w |= search16(scaled(x[k], fminf(row, col[k])), s.t.mv) << (4 * k);
+                }
+                *reinterpret_cast<uint32_t*>(codes + (e >> 1)) = w;
+            } else {
+                const uint32_t w = *reinterpret_cast<const uint32_t*>(codes + (e >> 1));
+                float x[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const f2 v = mul2(pair_lookup(s.qv2, w, j), mk2(fminf(row, col[2 * j]), fminf(row, col[2 * j + 1])));
+                    x[2 * j] = v.x;
+                    x[2 * j + 1] = v.y;
+                }
+                Elem<float>::store8(reinterpret_cast<char*>(out), e, x);
+            }
+        }
+    }
+}
+
 // Quantize / dequantize against finished row / column maxima; flat mapping over the matrix.
 template <bool QUANT>
 __global__ void __launch_bounds__(kThreads)
