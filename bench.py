@@ -352,6 +352,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=[None, *S.WORKLOADS, "quantize"])
+    ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "p2p"],
+                    help="N>1: how the updated parameters reach the other ranks (peer stores from the update kernel, or an all-gather)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

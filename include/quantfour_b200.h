@@ -30,9 +30,11 @@
 extern "C" {
 #endif
 
-#define QF_ABI_VERSION 2
+#define QF_ABI_VERSION 3
 #define QF_BLOCK 128        /* elements per quantization block (optim/cuda_adamw_kernels.cu:431) */
 #define QF_MAX_HYPERS 16    /* hyper-parameter sets one launch can carry */
+#define QF_MAX_PEERS 15     /* peer copies of the parameter buffer one launch can feed */
+#define QF_PEER_HANDLE_BYTES 64
 
 typedef enum QfStatus {
     QF_OK = 0,
@@ -130,6 +132,33 @@ int qf_step_pre(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers,
                 void* workspace, size_t workspace_bytes, int device, void* stream);
 int qf_step_main(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers,
                  void* workspace, size_t workspace_bytes, int device, void* stream);
+
+/*
+ * qf_step_main that also stores every updated parameter into the same place of up to QF_MAX_PEERS
+ * other devices' copies of the parameter buffer, from inside the update kernel: the all-gather of a
+ * sharded step rides the peer links while the update computes instead of following it.
+ * peer_delta_bytes[k] = (address at which peer k's buffer is mapped in this process) - (address of this
+ * device's buffer); every desc's p must lie in this device's buffer, and the peers' buffers must have the
+ * same layout.  The caller orders the launch after every peer's last read of its old parameters and
+ * lets no peer read the new ones before every device's launch has completed (one small collective on
+ * either side does both).  No counterpart in the reference, which has no sharding.
+ */
+int qf_step_main_push(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers,
+                      void* workspace, size_t workspace_bytes, int device, void* stream,
+                      const int64_t* peer_delta_bytes, int n_peers);
+
+/*
+ * Sharing a device buffer between the processes of one node (one process per device), for
+ * qf_step_main_push.  qf_peer_export writes an opaque handle of the allocation that holds `ptr` and the
+ * offset of `ptr` inside it; the bytes travel to the other process by any host channel; there
+ * qf_peer_open maps the allocation (enabling peer access) and returns its base, so the buffer is at
+ * base + offset; qf_peer_close unmaps it.  Opening a handle that is already open in the process returns the
+ * same mapping and counts it; the last qf_peer_close unmaps.  `ptr` must come from cudaMalloc (not from a
+ * virtual-memory pool).  No counterpart in the reference.
+ */
+int qf_peer_export(const void* ptr, int device, unsigned char handle[QF_PEER_HANDLE_BYTES], int64_t* offset_bytes);
+int qf_peer_open(const unsigned char handle[QF_PEER_HANDLE_BYTES], int device, void** base);
+int qf_peer_close(void* base, int device);
 
 /* Synchronise `stream`, read the status word kept in `workspace` into *status (QF_STATUS_* bits)
  * and clear it. */

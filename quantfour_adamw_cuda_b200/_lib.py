@@ -12,8 +12,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 # QUANTFOUR_B200_LIB may name another build of the same library (e.g. one compiled with different tuning macros).
 LIB_PATH = os.environ.get("QUANTFOUR_B200_LIB") or os.path.join(HERE, "libquantfour_b200.so")
 
-QF_ABI_VERSION = 2
+QF_ABI_VERSION = 3
 QF_MAX_HYPERS = 16
+QF_MAX_PEERS = 15
+QF_PEER_HANDLE_BYTES = 64
 QF_F32, QF_BF16 = 0, 1
 QF_KIND_FP32, QF_KIND_BLOCK, QF_KIND_RANK1 = 0, 1, 2
 QF_STATUS_NONFINITE = 1
@@ -46,6 +48,10 @@ _SIGNATURES = {
     "qf_step_multi": (C.c_int, _STEP_ARGS),
     "qf_step_pre": (C.c_int, _STEP_ARGS),
     "qf_step_main": (C.c_int, _STEP_ARGS),
+    "qf_step_main_push": (C.c_int, _STEP_ARGS + [C.POINTER(C.c_int64), C.c_int]),
+    "qf_peer_export": (C.c_int, [C.c_void_p, C.c_int, C.c_char_p, C.POINTER(C.c_int64)]),
+    "qf_peer_open": (C.c_int, [C.c_char_p, C.c_int, C.POINTER(C.c_void_p)]),
+    "qf_peer_close": (C.c_int, [C.c_void_p, C.c_int]),
     "qf_read_status": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.POINTER(C.c_uint32)]),
     "qf_fused_4bit": (C.c_int, [C.c_void_p] * 6 + [C.c_int64, C.c_int] + _SCALARS + [C.c_int, C.c_void_p]),
     "qf_fused_single_tensor": (C.c_int, [C.c_void_p] * 4 + [C.c_int64, C.c_int] + _SCALARS + [C.c_int, C.c_void_p]),

@@ -6,6 +6,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <string>
 #include <unordered_map>
 #include <vector>
 
@@ -241,20 +242,33 @@ int launch_pre(const Plan& pl, const qf::HyperPack& hp, cudaStream_t stream) {
     return QF_OK;
 }
 
-int launch_main(const Plan& pl, const qf::HyperPack& hp, cudaStream_t stream) {
-    if (pl.n == 0) return QF_OK;
-    if (pl.n_rank1) roll(pl, qf::kRollRecip, stream);
+template <bool PUSH>
+int launch_main_kernels(const Plan& pl, const qf::HyperPack& hp, const qf::PushPack& pp, cudaStream_t stream) {
     if (pl.items[kMainPanel]) {
         const int dyn = qf::main_dyn_smem(pl.any_f32_panel);
         const int ring = qf::kStages * (pl.any_f32_panel ? qf::kRowBytesF32 : qf::kRowBytesBf16);
-        QF_CUDA(cudaFuncSetAttribute(qf::step_main_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        QF_CUDA(cudaFuncSetAttribute(qf::step_main_kernel<true, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      qf::main_dyn_smem(true)));
-        qf::step_main_kernel<true><<<persistent_grid(pl.items[kMainPanel], QF_MAIN_MIN_CTAS), qf::kThreads, dyn, stream>>>(
-            pl.d_tensors, pl.d_base[kMainPanel], pl.n, hp, ring, pl.d_status);
+        qf::step_main_kernel<true, PUSH><<<persistent_grid(pl.items[kMainPanel], QF_MAIN_MIN_CTAS), qf::kThreads, dyn, stream>>>(
+            pl.d_tensors, pl.d_base[kMainPanel], pl.n, hp, ring, pl.d_status, pp);
     }
     if (pl.items[kMainFlat])
-        qf::step_main_kernel<false><<<persistent_grid(pl.items[kMainFlat], QF_MAIN_MIN_CTAS), qf::kThreads, 0, stream>>>(
-            pl.d_tensors, pl.d_base[kMainFlat], pl.n, hp, 0, pl.d_status);
+        qf::step_main_kernel<false, PUSH><<<persistent_grid(pl.items[kMainFlat], QF_MAIN_MIN_CTAS), qf::kThreads, 0, stream>>>(
+            pl.d_tensors, pl.d_base[kMainFlat], pl.n, hp, 0, pl.d_status, pp);
+    return QF_OK;
+}
+
+// `push`: null, or the peer copies of the parameter buffer the kernels also store into.
+int launch_main(const Plan& pl, const qf::HyperPack& hp, cudaStream_t stream, const qf::PushPack* push = nullptr) {
+    if (pl.n == 0) return QF_OK;
+    if (pl.n_rank1) roll(pl, qf::kRollRecip, stream);
+    if (push && push->n > 0) {
+        if (int rc = launch_main_kernels<true>(pl, hp, *push, stream)) return rc;
+    } else {
+        qf::PushPack none;
+        memset(&none, 0, sizeof none);
+        if (int rc = launch_main_kernels<false>(pl, hp, none, stream)) return rc;
+    }
     if (pl.n_rank1) roll(pl, qf::kRollCommit, stream);
     QF_CUDA(cudaGetLastError());
     return QF_OK;
@@ -279,7 +293,7 @@ qf::HyperDev widen_hyper(const QfHyper& h) {
 }
 
 int step_common(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,
-                size_t workspace_bytes, int device, void* stream, bool pre, bool main_) {
+                size_t workspace_bytes, int device, void* stream, bool pre, bool main_, const qf::PushPack* push = nullptr) {
     g_err[0] = 0;
     if (!hypers) return fail(QF_ERR_BAD_ARG, "hypers is null");
     QF_CUDA(cudaSetDevice(device));
@@ -292,7 +306,7 @@ int step_common(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers,
     if (pre)
         if (int rc = launch_pre(pl, hp, st)) return rc;
     if (main_)
-        if (int rc = launch_main(pl, hp, st)) return rc;
+        if (int rc = launch_main(pl, hp, st, push)) return rc;
     return QF_OK;
 }
 
@@ -345,6 +359,107 @@ int qf_step_pre(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers,
 int qf_step_main(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,
                  size_t workspace_bytes, int device, void* stream) {
     return step_common(descs, n_tensors, hypers, n_hypers, workspace, workspace_bytes, device, stream, false, true);
+}
+
+int qf_step_main_push(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,
+                      size_t workspace_bytes, int device, void* stream, const int64_t* peer_delta_bytes, int n_peers) {
+    g_err[0] = 0;
+    if (n_peers < 0 || n_peers > QF_MAX_PEERS) return fail(QF_ERR_BAD_ARG, "n_peers must be in 0..%d, got %d", QF_MAX_PEERS, n_peers);
+    if (n_peers > 0 && !peer_delta_bytes) return fail(QF_ERR_BAD_ARG, "peer_delta_bytes is null");
+    qf::PushPack pp;
+    memset(&pp, 0, sizeof pp);
+    pp.n = n_peers;
+    for (int k = 0; k < n_peers; ++k) {
+        // the vector path stores 16 bytes at p + delta whenever p itself is 16-byte aligned
+        if (peer_delta_bytes[k] == 0 || peer_delta_bytes[k] % 16)
+            return fail(QF_ERR_BAD_ARG, "peer %d: the distance to the peer buffer must be a non-zero multiple of 16 bytes", k);
+        pp.delta[k] = peer_delta_bytes[k];
+    }
+    return step_common(descs, n_tensors, hypers, n_hypers, workspace, workspace_bytes, device, stream, false, true, &pp);
+}
+
+// ---- sharing the parameter buffer between the processes of a node --------------------------------------------
+namespace {
+// Base of the allocation that holds `ptr`, through the driver entry point (the library links the runtime only).
+int allocation_base(const void* ptr, const void** base) {
+    typedef int (*RangeFn)(unsigned long long*, size_t*, unsigned long long);
+    static RangeFn fn = nullptr;
+    if (!fn) {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult st;
+        QF_CUDA(cudaGetDriverEntryPoint("cuMemGetAddressRange", &f, cudaEnableDefault, &st));
+        if (!f || st != cudaDriverEntryPointSuccess) return fail(QF_ERR_CUDA, "driver entry point cuMemGetAddressRange not found");
+        fn = reinterpret_cast<RangeFn>(f);
+    }
+    unsigned long long b = 0;
+    size_t size = 0;
+    const int rc = fn(&b, &size, static_cast<unsigned long long>(reinterpret_cast<uintptr_t>(ptr)));
+    if (rc != 0) return fail(QF_ERR_BAD_ARG, "pointer is not inside a device allocation (driver error %d)", rc);
+    *base = reinterpret_cast<const void*>(static_cast<uintptr_t>(b));
+    return QF_OK;
+}
+
+// An allocation can be mapped only once per process: mappings are shared and counted.
+struct PeerMapping {
+    void* base;
+    int refs;
+};
+std::mutex g_peer_mu;
+std::unordered_map<std::string, PeerMapping> g_peer_maps;  // key: device byte + handle bytes
+std::string peer_key(const unsigned char* handle, int device) {
+    std::string k(1, static_cast<char>(device));
+    k.append(reinterpret_cast<const char*>(handle), QF_PEER_HANDLE_BYTES);
+    return k;
+}
+}  // namespace
+
+int qf_peer_export(const void* ptr, int device, unsigned char* handle, int64_t* offset_bytes) {
+    g_err[0] = 0;
+    static_assert(sizeof(cudaIpcMemHandle_t) == QF_PEER_HANDLE_BYTES, "handle size");
+    if (!ptr || !handle || !offset_bytes) return fail(QF_ERR_BAD_ARG, "qf_peer_export: null argument");
+    QF_CUDA(cudaSetDevice(device));
+    const void* base = nullptr;
+    if (int rc = allocation_base(ptr, &base)) return rc;
+    cudaIpcMemHandle_t h;
+    QF_CUDA(cudaIpcGetMemHandle(&h, const_cast<void*>(base)));
+    memcpy(handle, &h, sizeof h);
+    *offset_bytes = static_cast<const char*>(ptr) - static_cast<const char*>(base);
+    return QF_OK;
+}
+
+int qf_peer_open(const unsigned char* handle, int device, void** base) {
+    g_err[0] = 0;
+    if (!handle || !base) return fail(QF_ERR_BAD_ARG, "qf_peer_open: null argument");
+    QF_CUDA(cudaSetDevice(device));
+    std::lock_guard<std::mutex> lock(g_peer_mu);
+    const std::string key = peer_key(handle, device);
+    auto it = g_peer_maps.find(key);
+    if (it != g_peer_maps.end()) {
+        ++it->second.refs;
+        *base = it->second.base;
+        return QF_OK;
+    }
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof h);
+    QF_CUDA(cudaIpcOpenMemHandle(base, h, cudaIpcMemLazyEnablePeerAccess));
+    g_peer_maps[key] = PeerMapping{*base, 1};
+    return QF_OK;
+}
+
+int qf_peer_close(void* base, int device) {
+    g_err[0] = 0;
+    if (!base) return QF_OK;
+    QF_CUDA(cudaSetDevice(device));
+    std::lock_guard<std::mutex> lock(g_peer_mu);
+    for (auto it = g_peer_maps.begin(); it != g_peer_maps.end(); ++it) {
+        if (it->second.base != base || it->first[0] != static_cast<char>(device)) continue;
+        if (--it->second.refs == 0) {
+            g_peer_maps.erase(it);
+            QF_CUDA(cudaIpcCloseMemHandle(base));
+        }
+        return QF_OK;
+    }
+    return fail(QF_ERR_BAD_ARG, "qf_peer_close: %p is not a mapping qf_peer_open returned", base);
 }
 
 int qf_read_status(void* workspace, int device, void* stream, uint32_t* status) {

@@ -71,6 +71,20 @@ struct HyperPack {
     HyperDev h[QF_MAX_HYPERS];
 };
 
+// Peer copies of the parameter buffer (sharded step): every updated parameter vector is stored at
+// p + delta[k] as well, k < n, where delta[k] is the byte distance from this device's parameter buffer to
+// the mapping of peer k's buffer.  The stores ride the peer links while the update computes.
+struct PushPack {
+    int32_t n;
+    int32_t pad;
+    int64_t delta[QF_MAX_PEERS];
+};
+template <typename T>
+__device__ __forceinline__ void push_store8(char* base, int64_t e, const float (&x)[8], const PushPack* push) {
+    const int n = push->n;
+    for (int k = 0; k < n; ++k) Elem<T>::store8(base + push->delta[k], e, x);
+}
+
 // ---- first-moment search table ------------------------------------------------------------------------
 // Index = sign, exponent and two mantissa bits of x (bits 31..21).  The floats that share an index form an
 // interval that holds at most one of the 15 midpoints, so code(x) = base[index] + (thr[index] < x), with
@@ -398,7 +412,7 @@ __device__ __forceinline__ void pre_panel(const DevTensor& t, int64_t li, const 
 // of line and self-contained (it reloads its column maxima) so that it costs the hot loop no registers.
 template <typename T>
 __device__ __noinline__ void main_panel_row_exact(const DevTensor* tp, int64_t e, int r, int j0, const HyperDev& hd,
-                                                  const Smem& s, uint32_t* status) {
+                                                  const Smem& s, uint32_t* status, const PushPack* push) {
     const DevTensor t = *tp;
     const int lane = threadIdx.x & 31;
     uint8_t* mc = reinterpret_cast<uint8_t*>(t.m);
@@ -420,6 +434,7 @@ __device__ __noinline__ void main_panel_row_exact(const DevTensor* tp, int64_t e
         adamw_elem(p[k], g[k], m[k], v[k], hd.h);
     }
     Elem<T>::store8(t.p, e, p);
+    if (push) push_store8<T>(t.p, e, p, push);
     const float ms_new = absmax8_bits_to_block(m);
     *reinterpret_cast<uint32_t*>(mc + (e >> 1)) = quantize8(m, ms_new, s.t.mm, 8);
     if ((lane & 15) == 0) {
@@ -449,9 +464,9 @@ constexpr int kColBytes = 3 * 4 * 32 * 8;              // per warp: old / new / 
 // L1 to the CTA, which the measurements reward.
 constexpr int main_dyn_smem(bool any_f32) { return kWarpsPerCta * (kStages * (any_f32 ? kRowBytesF32 : kRowBytesBf16) + kColBytes); }
 
-template <typename T>
+template <typename T, bool PUSH>
 __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, const HyperDev& hd, const Smem& s,
-                                           char* stage, int ring_bytes, uint32_t* status) {
+                                           char* stage, int ring_bytes, uint32_t* status, const PushPack* push) {
     const DevTensor t = *tp;
     const int lane = threadIdx.x & 31;
     const int band = static_cast<int>(li / t.panels);
@@ -539,7 +554,7 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
         const char* base = stage + slot * kRowBytes;
         slot = slot + 1 == kStages ? 0 : slot + 1;
         if (!(col_fast && sc.rrow == sc.rrow && sc.row_old > 0.0f)) {  // warp-uniform
-            main_panel_row_exact<T>(tp, e, r, j0, hd, s, status);
+            main_panel_row_exact<T>(tp, e, r, j0, hd, s, status, PUSH ? push : nullptr);
             continue;
         }
         Raw8<T> praw, graw;
@@ -571,6 +586,7 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
             wq += code_from_y(y.y) << (8 * j + 4);
         }
         Elem<T>::store8(t.p, e, p);
+        if (PUSH) push_store8<T>(t.p, e, p, push);
         *reinterpret_cast<uint32_t*>(vc + (e >> 1)) = wq;
         const float ms_new = absmax_pairs_to_block(m);
         *reinterpret_cast<uint32_t*>(mc + (e >> 1)) = quantize_m8(m, ms_new, s);
@@ -604,6 +620,12 @@ __device__ __forceinline__ void store8_masked(char* base, int64_t e, int nv, boo
         for (int k = 0; k < 8; ++k)
             if (k < nv) Elem<T>::store1(base, e + k, x[k]);
     }
+}
+template <typename T>
+__device__ __forceinline__ void push_store8_masked(char* base, int64_t e, int nv, bool vec, const float (&x)[8],
+                                                   const PushPack* push) {
+    const int n = push->n;
+    for (int k = 0; k < n; ++k) store8_masked<T>(base + push->delta[k], e, nv, vec, x);
 }
 __device__ __forceinline__ uint32_t load_codes(const uint8_t* c, int64_t e, int nv, bool vec) {
     return (vec && nv == 8) ? *reinterpret_cast<const uint32_t*>(c + (e >> 1)) : load_codes_tail(c, e, nv);
@@ -665,7 +687,7 @@ __device__ __forceinline__ void pre_flat_rank1(const DevTensor& t, int64_t li, c
 // One run of 256 flattened elements, exact arithmetic, any tail, any alignment.
 template <typename T, int KIND>
 __device__ __noinline__ void main_flat_run_exact(const DevTensor* tp, int64_t wbase, const HyperDev& hd, const Smem& s,
-                                                 uint32_t* status) {
+                                                 uint32_t* status, const PushPack* push) {
     const DevTensor t = *tp;
     const int lane = threadIdx.x & 31;
     const bool vec = t.flags & kFlagVec;
@@ -682,6 +704,7 @@ __device__ __noinline__ void main_flat_run_exact(const DevTensor* tp, int64_t wb
 #pragma unroll
         for (int k = 0; k < 8; ++k) adamw_elem(p[k], g[k], m[k], v[k], hd.h);
         store8_masked<T>(t.p, e, nv, vec, p);
+        if (push) push_store8_masked<T>(t.p, e, nv, vec, p, push);
         store8_masked<float>(t.m, e, nv, vec, m);
         store8_masked<float>(t.v, e, nv, vec, v);
         return;
@@ -714,6 +737,7 @@ __device__ __noinline__ void main_flat_run_exact(const DevTensor* tp, int64_t wb
         }
     }
     store8_masked<T>(t.p, e, nv, vec, p);
+    if (push) push_store8_masked<T>(t.p, e, nv, vec, p, push);
     const float ms_new = absmax8_bits_to_block(m);  // all 32 lanes take part in the shuffles
     float vs_new = 0.0f;
     if (KIND == QF_KIND_BLOCK) vs_new = absmax8_bits_to_block(v);
@@ -737,7 +761,7 @@ __device__ __noinline__ void main_flat_run_exact(const DevTensor* tp, int64_t wb
 // One full, vector-aligned run of 256 elements with the packed arithmetic (block-128 and fp32-state kinds).
 template <typename T, int KIND>
 __device__ __forceinline__ void main_flat_run_fast(const DevTensor& t, int64_t wbase, const Hyper2& h2, const Smem& s,
-                                                   uint32_t* status) {
+                                                   uint32_t* status, const PushPack* push) {
     const int lane = threadIdx.x & 31;
     const int64_t e = wbase + lane * 8;
     float p[8], g[8];
@@ -756,6 +780,7 @@ __device__ __forceinline__ void main_flat_run_fast(const DevTensor& t, int64_t w
             v[2 * j] = vv.x; v[2 * j + 1] = vv.y;
         }
         Elem<T>::store8(t.p, e, p);
+        if (push) push_store8<T>(t.p, e, p, push);
         Elem<float>::store8(t.m, e, m);
         Elem<float>::store8(t.v, e, v);
         return;
@@ -778,6 +803,7 @@ __device__ __forceinline__ void main_flat_run_fast(const DevTensor& t, int64_t w
         p[2 * j + 1] = pp.y;
     }
     Elem<T>::store8(t.p, e, p);
+    if (push) push_store8<T>(t.p, e, p, push);
     const float ms_new = absmax_pairs_to_block(m);
     const float vs_new = absmax_pairs_to_block(v);
     *reinterpret_cast<uint32_t*>(mc + (e >> 1)) = quantize_m8(m, ms_new, s);
@@ -803,7 +829,7 @@ __device__ __forceinline__ void main_flat_run_fast(const DevTensor& t, int64_t w
 
 template <typename T, int KIND>
 __device__ __forceinline__ void main_flat(const DevTensor* tp, int64_t li, const HyperDev& hd, const Smem& s,
-                                          uint32_t* status) {
+                                          uint32_t* status, const PushPack* push) {
     const DevTensor t = *tp;
     const bool vec = t.flags & kFlagVec;
     const int64_t start = li * (kPanelCols * kRowsPerItem);
@@ -812,9 +838,9 @@ __device__ __forceinline__ void main_flat(const DevTensor* tp, int64_t li, const
         const int64_t wbase = start + static_cast<int64_t>(it) * kPanelCols;
         if (wbase >= t.numel) break;  // warp-uniform
         if (KIND != QF_KIND_RANK1 && hd.fast && vec && wbase + kPanelCols <= t.numel)
-            main_flat_run_fast<T, KIND>(t, wbase, h2, s, status);
+            main_flat_run_fast<T, KIND>(t, wbase, h2, s, status, push);
         else
-            main_flat_run_exact<T, KIND>(tp, wbase, hd, s, status);
+            main_flat_run_exact<T, KIND>(tp, wbase, hd, s, status, push);
     }
 }
 
@@ -858,23 +884,26 @@ step_pre_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict
 
 template <typename T>
 __device__ __forceinline__ void main_flat_dispatch(const DevTensor* tp, int64_t li, const HyperDev& h, const Smem& s,
-                                                   uint32_t* status) {
+                                                   uint32_t* status, const PushPack* push) {
     const int kind = tp->kind;
     if (kind == QF_KIND_RANK1)
-        main_flat<T, QF_KIND_RANK1>(tp, li, h, s, status);
+        main_flat<T, QF_KIND_RANK1>(tp, li, h, s, status, push);
     else if (kind == QF_KIND_BLOCK)
-        main_flat<T, QF_KIND_BLOCK>(tp, li, h, s, status);
+        main_flat<T, QF_KIND_BLOCK>(tp, li, h, s, status, push);
     else
-        main_flat<T, QF_KIND_FP32>(tp, li, h, s, status);
+        main_flat<T, QF_KIND_FP32>(tp, li, h, s, status, push);
 }
 
 #ifndef QF_MAIN_MIN_CTAS
 #define QF_MAIN_MIN_CTAS 2
 #endif
-template <bool PANEL>
+// PUSH: the launch also stores every updated parameter vector into the peers' buffers named by `pp`.
+template <bool PANEL, bool PUSH>
 __global__ void __launch_bounds__(kThreads, QF_MAIN_MIN_CTAS)
 step_main_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict__ base, int n,
-                 const __grid_constant__ HyperPack hp, int ring_bytes, uint32_t* status) {
+                 const __grid_constant__ HyperPack hp, int ring_bytes, uint32_t* status,
+                 const __grid_constant__ PushPack pp) {
+    const PushPack* push = PUSH ? &pp : nullptr;
     __shared__ Smem s;
     load_smem(s);
     extern __shared__ __align__(16) char staging[];  // panel kernel: per warp a ring of rows plus the column block
@@ -887,14 +916,14 @@ step_main_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restric
         const HyperDev& h = hp.h[tp->hyper];  // hp is a grid constant: its address is usable as it is
         if (PANEL) {
             if (tp->dtype == QF_BF16)
-                main_panel<__nv_bfloat16>(tp, li, h, s, stage, ring_bytes, status);
+                main_panel<__nv_bfloat16, PUSH>(tp, li, h, s, stage, ring_bytes, status, push);
             else
-                main_panel<float>(tp, li, h, s, stage, ring_bytes, status);
+                main_panel<float, PUSH>(tp, li, h, s, stage, ring_bytes, status, push);
         } else {
             if (tp->dtype == QF_BF16)
-                main_flat_dispatch<__nv_bfloat16>(tp, li, h, s, status);
+                main_flat_dispatch<__nv_bfloat16>(tp, li, h, s, status, push);
             else
-                main_flat_dispatch<float>(tp, li, h, s, status);
+                main_flat_dispatch<float>(tp, li, h, s, status, push);
         }
     }
 }
@@ -909,9 +938,9 @@ single_tensor_kernel(const __grid_constant__ DevTensor t, const __grid_constant_
     const int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
     if (item * (kPanelCols * kRowsPerItem) >= t.numel) return;
     if (t.dtype == QF_BF16)
-        main_flat_dispatch<__nv_bfloat16>(&t, item, h, s, &g_unread_status);
+        main_flat_dispatch<__nv_bfloat16>(&t, item, h, s, &g_unread_status, nullptr);
     else
-        main_flat_dispatch<float>(&t, item, h, s, &g_unread_status);
+        main_flat_dispatch<float>(&t, item, h, s, &g_unread_status, nullptr);
 }
 
 // Small passes over the row / column maxima of every rank-1 tensor.  One CTA per (tensor, slice).

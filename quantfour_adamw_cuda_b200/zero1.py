@@ -7,7 +7,11 @@ Layout.  All parameters (in optimizer order) are laid out in one flat buffer; ev
 multiple of 128 elements so that its 128-element quantization blocks coincide with blocks of the flat
 space.  The flat space is cut into `world` equal ranges of `shard` elements (a multiple of 128).  Rank r
 owns the optimizer state of range r and updates the parameters in it; parameters and gradients stay
-replicated.  After the step each rank's range is all-gathered in place into every rank's flat buffer.
+replicated.  After the step each rank's range is all-gathered in place into every rank's flat buffer
+(`comm="nccl"`), or -- when the ranks are processes of one node whose devices reach one another's memory
+(`comm="p2p"`, what `comm="auto"` picks if the set-up succeeds on every rank) -- the update kernel itself stores
+each new parameter vector into every peer's flat buffer over NVLink while it computes, and no all-gather
+follows (qf_step_main_push).
 
 A 2-D tensor cut by a range boundary keeps its rank-1 second-moment scales identical to the unsharded
 optimizer: the new row / column maxima of such a tensor are combined with an element-wise max over the
@@ -176,20 +180,42 @@ class CudaBackend:
             self.ws = torch.zeros(need, dtype=torch.uint8, device=dev)
         self.descs, self.sig = descs, sig
 
-    def _call(self, fn, states: List[RecordState], hyper: _lib.QfHyper) -> None:
+    def _call(self, fn, states: List[RecordState], hyper: _lib.QfHyper, *extra) -> None:
         if not states:
             return
         self._prepare(states)
         dev = states[0].p.device
         harr = (_lib.QfHyper * 1)(hyper)
         _lib.check(fn(self.descs, len(self.descs), harr, 1, self.ws.data_ptr(), self.ws.numel(), dev.index,
-                      C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)), "sharded step")
+                      C.c_void_p(torch.cuda.current_stream(dev).cuda_stream), *extra), "sharded step")
 
     def pre(self, states: List[RecordState], hyper: _lib.QfHyper) -> None:
         self._call(self.L.qf_step_pre, states, hyper)
 
     def main(self, states: List[RecordState], hyper: _lib.QfHyper) -> None:
         self._call(self.L.qf_step_main, states, hyper)
+
+    def main_push(self, states: List[RecordState], hyper: _lib.QfHyper, deltas: Sequence[int]) -> None:
+        """`main` that also stores the new parameters at the same place of every peer's flat buffer."""
+        arr = (C.c_int64 * len(deltas))(*deltas)
+        self._call(self.L.qf_step_main_push, states, hyper, arr, len(deltas))
+
+    # ---- the flat buffer in the other processes of the node -----------------------------------------
+
+    def export_buffer(self, t: torch.Tensor) -> Tuple[bytes, int]:
+        handle = C.create_string_buffer(_lib.QF_PEER_HANDLE_BYTES)
+        off = C.c_int64(0)
+        _lib.check(self.L.qf_peer_export(C.c_void_p(t.data_ptr()), t.device.index, handle, C.byref(off)), "qf_peer_export")
+        return handle.raw, off.value
+
+    def open_buffer(self, handle: bytes, offset: int, device: torch.device) -> Tuple[int, int]:
+        """(base of the mapping, address of the peer's buffer in this process)."""
+        base = C.c_void_p(0)
+        _lib.check(self.L.qf_peer_open(handle, device.index, C.byref(base)), "qf_peer_open")
+        return base.value, base.value + offset
+
+    def close_buffer(self, base: int, device: torch.device) -> None:
+        _lib.check(self.L.qf_peer_close(C.c_void_p(base), device.index), "qf_peer_close")
 
 
 class ShardedFourBitAdamW(torch.optim.Optimizer):
@@ -202,7 +228,7 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
 
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, *, fused: Optional[bool] = False,
                  quant_threshold: int = DEFAULT_THRESHOLD, process_group=None, backend=None,
-                 rank: Optional[int] = None, world: Optional[int] = None):
+                 rank: Optional[int] = None, world: Optional[int] = None, comm: str = "auto"):
         if not 0.0 < lr:
             raise ValueError(f"Invalid learning rate: {lr=}")
         if not 0.0 < eps:
@@ -234,8 +260,15 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
             raise TypeError(f"parameters must be float32 or bfloat16, got {p0.dtype}")
         self.layout = flat_layout([p.shape for p in self.params], self.world)
         self.step_count = 0
+        if comm not in ("auto", "nccl", "p2p"):
+            raise ValueError(f"comm must be 'auto', 'nccl' or 'p2p', got {comm!r}")
         self._flatten()
         self._build_state()
+        self.peer_deltas: List[int] = []
+        self._peer_bases: List[int] = []
+        self.comm = "nccl"
+        if comm != "nccl" and self.sharded and self.world > 1 and self.flat.is_cuda:
+            self._setup_p2p(required=comm == "p2p")
 
     # ---- set-up -----------------------------------------------------------------------------------
 
@@ -296,6 +329,49 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
                     st.v_col, st.col_new, st.col_rcp = old[Rp:Rp + Cc], new[Rp:Rp + Cc], rcp[Rp:Rp + Cc]
             self.states.append(st)
 
+    def _setup_p2p(self, required: bool) -> None:
+        """Map every other rank's flat buffer into this process.  All ranks take the same decision: one
+        failure anywhere (devices of different nodes, no peer access, a virtual-memory allocator) keeps the
+        all-gather."""
+        dev = self.flat.device
+        self._token = torch.zeros(1, dtype=torch.float32, device=dev)
+        err, mine = "", None
+        try:
+            mine = self.backend.export_buffer(self.flat)
+        except Exception as e:  # noqa: BLE001 - any failure means: no peer path
+            err = f"{type(e).__name__}: {e}"
+        everyone: List[Any] = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=self.group)
+        if not err and all(x is not None for x in everyone) and self.world - 1 <= _lib.QF_MAX_PEERS:
+            try:
+                for r, (handle, off) in enumerate(everyone):
+                    if r == self.rank:
+                        continue
+                    base, addr = self.backend.open_buffer(handle, off, dev)
+                    self._peer_bases.append(base)
+                    self.peer_deltas.append(addr - self.flat.data_ptr())
+            except Exception as e:  # noqa: BLE001
+                err = f"{type(e).__name__}: {e}"
+        elif not err:
+            err = "a peer could not export its buffer"
+        ok = torch.tensor([0.0 if err else 1.0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        if ok.item() == 1.0:
+            self.comm = "p2p"
+            return
+        self.close()
+        if required:
+            raise RuntimeError(f"comm='p2p' is not available on rank {self.rank}: {err or 'another rank failed'}")
+
+    def close(self) -> None:
+        """Unmap the peers' buffers (the optimizer falls back to the all-gather afterwards)."""
+        for base in self._peer_bases:
+            try:
+                self.backend.close_buffer(base, self.flat.device)
+            except Exception:  # noqa: BLE001 - shutting down
+                pass
+        self._peer_bases, self.peer_deltas, self.comm = [], [], "nccl"
+
     # ---- step -------------------------------------------------------------------------------------
 
     @torch.no_grad()
@@ -305,11 +381,21 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
             with torch.enable_grad():
                 loss = closure()
         self.step_pre()
-        if self.sharded and self.world > 1 and self.shared_new.numel():
+        multi = self.sharded and self.world > 1
+        if multi and self.shared_new.numel():
             # element-wise max of the new row / column maxima of the tensors that are cut between ranks
             dist.all_reduce(self.shared_new, op=dist.ReduceOp.MAX, group=self.group)
+        if multi and self.comm == "p2p":
+            if not self.shared_new.numel():
+                dist.all_reduce(self._token, op=dist.ReduceOp.MAX, group=self.group)
+            # the collective above has put every rank's earlier work (its last reads of the old parameters)
+            # before any rank's stores into it; the one below keeps every rank from reading the new
+            # parameters before all ranks' kernels, and with them their stores, have completed
+            self.backend.main_push(self.states, self._hyper, self.peer_deltas)
+            dist.all_reduce(self._token, op=dist.ReduceOp.MAX, group=self.group)
+            return loss
         self.step_main()
-        if self.sharded and self.world > 1:
+        if multi:
             self._all_gather()
         return loss
 

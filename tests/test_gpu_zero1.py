@@ -67,3 +67,51 @@ def test_emulated_ranks_match_unsharded_oracle(world, dtype):
     for params, _ in ranks:
         for i, (p, w) in enumerate(zip(params, want)):
             assert torch.equal(p.detach().cpu(), w), f"tensor {i} {SHAPES[i]} differs in {(p.detach().cpu() != w).sum()} places"
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_emulated_ranks_with_peer_stores(world, dtype):
+    """qf_step_main_push with the other ranks' flat buffers standing in for peer mappings (same device):
+    the stores issued by the update kernels replace the all-gather."""
+    init, grads, want = _oracle_run(dtype, 4, 2)
+    ranks = []
+    for r in range(world):
+        params = [torch.nn.Parameter(p.cuda()) for p in init]
+        ranks.append((params, ShardedFourBitAdamW(params, lr=1e-3, rank=r, world=world)))
+    for gs in grads:
+        for params, opt in ranks:
+            for p, g in zip(params, gs):
+                p.grad = g.cuda()
+            opt.step_pre()
+        if ranks[0][1].shared_new.numel():
+            combined = torch.stack([opt.shared_new for _, opt in ranks]).max(dim=0).values
+            for _, opt in ranks:
+                opt.shared_new.copy_(combined)
+        for _, opt in ranks:
+            deltas = [other.flat.data_ptr() - opt.flat.data_ptr() for _, other in ranks if other is not opt]
+            opt.backend.main_push(opt.states, opt._hyper, deltas)
+    torch.cuda.synchronize()
+    for params, _ in ranks:
+        for i, (p, w) in enumerate(zip(params, want)):
+            assert torch.equal(p.detach().cpu(), w), f"tensor {i} {SHAPES[i]} differs in {(p.detach().cpu() != w).sum()} places"
+
+
+def test_push_rejects_bad_peers():
+    params = [torch.nn.Parameter(torch.zeros(64, 256, device="cuda"))]
+    opt = ShardedFourBitAdamW(params, lr=1e-3)
+    params[0].grad = torch.zeros_like(params[0])
+    opt.step_pre()
+    with pytest.raises(ValueError, match="n_peers"):
+        opt.backend.main_push(opt.states, opt._hyper, [1024] * 16)
+    with pytest.raises(ValueError, match="multiple of 16"):
+        opt.backend.main_push(opt.states, opt._hyper, [8])
+    opt.step_main()
+
+
+def test_peer_export_reports_offset():
+    """The handle of a buffer inside a larger allocation comes with the buffer's offset in it."""
+    from quantfour_adamw_cuda_b200.zero1 import CudaBackend
+    big = torch.zeros(1 << 22, dtype=torch.uint8, device="cuda")
+    handle, off = CudaBackend().export_buffer(big[4096:])
+    assert len(handle) == 64 and off >= 4096 and (off - 4096) % 512 == 0

@@ -1,0 +1,65 @@
+"""Two processes on two GPUs: the sharded step with the parameters delivered by peer stores from the update
+kernel (comm="p2p") must leave the same bits as the all-gather path (comm="nccl") and as the unsharded oracle.
+Skipped on a single-GPU machine."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["QF_ROOT"])
+from oracle import c_oracle as CO, torch_oracle as TO
+from quantfour_adamw_cuda_b200.zero1 import ShardedFourBitAdamW
+rank, local = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
+dev = torch.device("cuda", local)
+torch.cuda.set_device(dev)
+dist.init_process_group("nccl", device_id=dev)
+SHAPES = [(300, 256), (1000,), (96, 128), (5000,), (64, 77), (1024, 512), (130, 384), (4096,), (512, 512)]
+HP = (1e-3, 0.9, 0.999, 1e-8, 0.01)
+for dtype in (torch.bfloat16, torch.float32):
+    gen = torch.Generator().manual_seed(5)
+    init = [(torch.randn(s, generator=gen) * 0.02).to(dtype) for s in SHAPES]
+    want = [p.clone() for p in init]
+    states = [TO.TensorState.zeros(s) for s in SHAPES]
+    runs = {}
+    for comm in ("p2p", "nccl"):
+        params = [torch.nn.Parameter(p.to(dev)) for p in init]
+        runs[comm] = (params, ShardedFourBitAdamW(params, lr=1e-3, comm=comm))
+        assert runs[comm][1].comm == comm, (comm, runs[comm][1].comm)
+    for step in range(5):
+        gs = [(torch.randn(s, generator=gen) * 1e-3).to(dtype) for s in SHAPES]
+        for p, g, st in zip(want, gs, states):
+            CO.step_tensor(p, g, st, *HP)
+        for params, opt in runs.values():
+            for p, g in zip(params, gs):
+                p.grad = g.to(dev)
+            opt.step()
+    torch.cuda.synchronize(dev)
+    for comm, (params, opt) in runs.items():
+        for i, (p, w) in enumerate(zip(params, want)):
+            assert torch.equal(p.detach().cpu(), w), f"rank {rank} {comm} {dtype} tensor {i} {SHAPES[i]}"
+    assert torch.equal(runs["p2p"][1].flat, runs["nccl"][1].flat)
+    runs["p2p"][1].close()
+dist.barrier()
+dist.destroy_process_group()
+print(f"rank {rank} ok")
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_stores_match_all_gather(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, QF_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29631", str(script)]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert "rank 0 ok" in out.stdout and "rank 1 ok" in out.stdout
