@@ -507,7 +507,7 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
     // The pass that stored the reciprocals wrote NaN where an old or new maximum is outside the range of
     // the fast sequences.  A zero old maximum (first step, rows never touched) lets v fall below the range
     // of the unchecked square root, so such rows and columns take the exact path as well.
-    f2* colbuf = reinterpret_cast<f2*>(stage + ring_bytes) + lane;  // [old | -new | 1/new][pair][lane]
+    float4* colbuf = reinterpret_cast<float4*>(stage + ring_bytes) + lane;  // [old | -new | 1/new][half][lane]
     bool ok = hd.fast;
     {
         float col_old[8], col_new[8], rcol[8];
@@ -517,10 +517,10 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
 #pragma unroll
         for (int k = 0; k < 8; ++k) ok &= rcol[k] == rcol[k] && col_old[k] > 0.0f;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            colbuf[(0 * 4 + j) * 32] = mk2(col_old[2 * j], col_old[2 * j + 1]);
-            colbuf[(1 * 4 + j) * 32] = mk2(-col_new[2 * j], -col_new[2 * j + 1]);
-            colbuf[(2 * 4 + j) * 32] = mk2(rcol[2 * j], rcol[2 * j + 1]);
+        for (int j = 0; j < 2; ++j) {
+            colbuf[(0 * 2 + j) * 32] = make_float4(col_old[4 * j], col_old[4 * j + 1], col_old[4 * j + 2], col_old[4 * j + 3]);
+            colbuf[(1 * 2 + j) * 32] = make_float4(-col_new[4 * j], -col_new[4 * j + 1], -col_new[4 * j + 2], -col_new[4 * j + 3]);
+            colbuf[(2 * 2 + j) * 32] = make_float4(rcol[4 * j], rcol[4 * j + 1], rcol[4 * j + 2], rcol[4 * j + 3]);
         }
     }
     const bool col_fast = __all_sync(kFull, ok);
@@ -573,7 +573,13 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
         for (int j = 0; j < 4; ++j) {
             f2 pp = mk2(p[2 * j], p[2 * j + 1]);
             m[j] = mul2(pair_lookup(s.qm2, wm, j), ms_old);
-            const f2 co = colbuf[(0 * 4 + j) * 32], ncn = colbuf[(1 * 4 + j) * 32], rcn = colbuf[(2 * 4 + j) * 32];
+            f2 co, ncn, rcn;
+            {
+                const float4 a = colbuf[(0 * 2 + (j >> 1)) * 32], b = colbuf[(1 * 2 + (j >> 1)) * 32], c = colbuf[(2 * 2 + (j >> 1)) * 32];
+                co = (j & 1) ? mk2(a.z, a.w) : mk2(a.x, a.y);
+                ncn = (j & 1) ? mk2(b.z, b.w) : mk2(b.x, b.y);
+                rcn = (j & 1) ? mk2(c.z, c.w) : mk2(c.x, c.y);
+            }
             f2 v = mul2(pair_lookup(s.qv2, wv, j), mk2(fminf(row_old, co.x), fminf(row_old, co.y)));
             adamw_pair<true>(pp, mk2(g[2 * j], g[2 * j + 1]), m[j], v, h2);
             p[2 * j] = pp.x;
