@@ -106,8 +106,8 @@ int qf_abi_version(void);
 const char* qf_last_error(void);
 
 /* Bytes of device workspace a step over n_tensors tensors needs.  The workspace holds the device
- * copy of the descriptor table and the status word; the library treats its contents as its own
- * between calls (it skips the upload when the table has not changed). */
+ * copy of the descriptor table (rewritten by every call, on the call's stream) and the status word,
+ * which accumulates between calls until qf_read_status clears it: hand in zero-filled memory. */
 size_t qf_workspace_bytes(int n_tensors);
 
 /*

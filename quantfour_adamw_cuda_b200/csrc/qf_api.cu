@@ -45,10 +45,12 @@ int64_t flat_items(int64_t numel) {
     return (numel + per - 1) / per;
 }
 
-// What the library remembers about a workspace: the table it last uploaded there and a pair of
-// pinned staging buffers so that an upload never has to wait for the stream.
+// What the library keeps per workspace: a pair of pinned staging buffers so that the upload of the table
+// never has to wait for the stream.  The table is uploaded on every call: remembering "this table is already
+// there" would be wrong as soon as the caller recycles the memory (a freed workspace whose address comes back
+// from the allocator zero-filled, with descriptors that happen to be identical), and the copy is a few tens of
+// kilobytes on the launch stream.
 struct WsCache {
-    std::vector<char> last;
     char* pinned[2] = {nullptr, nullptr};
     cudaEvent_t ev[2] = {nullptr, nullptr};
     size_t cap = 0;
@@ -167,14 +169,8 @@ int build_plan(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* wor
     if (n == 0) return QF_OK;
 
     const size_t bytes = table_bytes(n);
-    std::vector<char> host(bytes);
-    memcpy(host.data(), tab.data(), tensors_bytes);
-    for (int k = 0; k < kTables; ++k)
-        memcpy(host.data() + tensors_bytes + static_cast<size_t>(k) * (n + 1) * 8, base[k].data(), (n + 1) * 8);
-
     std::lock_guard<std::mutex> lock(g_mu);
     WsCache& c = g_cache[(static_cast<uint64_t>(device) << 56) ^ reinterpret_cast<uint64_t>(workspace)];
-    if (c.last.size() == bytes && memcmp(c.last.data(), host.data(), bytes) == 0) return QF_OK;
     if (c.cap < bytes) {
         for (int k = 0; k < 2; ++k) {
             if (c.pinned[k]) cudaFreeHost(c.pinned[k]);
@@ -186,11 +182,12 @@ int build_plan(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* wor
     }
     const int k = c.cur ^ 1;
     QF_CUDA(cudaEventSynchronize(c.ev[k]));  // the copy that last used this staging buffer has finished
-    memcpy(c.pinned[k], host.data(), bytes);
+    memcpy(c.pinned[k], tab.data(), tensors_bytes);
+    for (int t = 0; t < kTables; ++t)
+        memcpy(c.pinned[k] + tensors_bytes + static_cast<size_t>(t) * (n + 1) * 8, base[t].data(), (n + 1) * 8);
     QF_CUDA(cudaMemcpyAsync(ws + kStatusBytes, c.pinned[k], bytes, cudaMemcpyHostToDevice, stream));
     QF_CUDA(cudaEventRecord(c.ev[k], stream));
     c.cur = k;
-    c.last.swap(host);
     return QF_OK;
 }
 

@@ -170,10 +170,13 @@ __device__ __forceinline__ uint32_t search_m_lut(float x, const LutEntry* lut) {
 
 // Second-moment map: midpoints are (1.5 + k) / 16, so the count of midpoints below x is ceil(16 x - 1.5)
 // clamped to 0..15; 16 x - 1.5 is exact wherever it is positive.
+// CLAMP = false is for callers whose x cannot exceed 1 (the scale is a maximum over values that include the
+// dividend, taken by the same kernel sequence): 16 x - 1.5 <= 14.5 then, and the code needs no upper clamp.
+template <bool CLAMP = true>
 __device__ __forceinline__ uint32_t code_from_y(float y) {
     uint32_t c;
     asm("cvt.rpi.u32.f32 %0, %1;" : "=r"(c) : "f"(y));  // saturating: negative and NaN -> 0
-    return min(c, 15u);
+    return CLAMP ? min(c, 15u) : c;
 }
 __device__ __forceinline__ uint32_t search_v_closed(float x) { return code_from_y(__fmaf_rn(x, 16.0f, -1.5f)); }
 
@@ -360,15 +363,16 @@ __device__ __forceinline__ void pre_panel(const DevTensor& t, int64_t li, const 
     uint32_t cmax[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) cmax[k] = 0;
-    int slot = 0;
-    for (int r = r0; r < r1; ++r) {
+    // Row maxima stay in registers until the item ends: lane k keeps the maxima of rows r0 + k and r0 + 32 + k,
+    // which then go out as two warp-wide reductions instead of one single-lane atomic per row.
+    uint32_t keep_lo = 0, keep_hi = 0;
+    auto body = [&](int r, int slot) {  // `slot` is a compile-time constant in the unrolled groups below
         if (r_issue < r1) issue(e_issue, slot == 0 ? kPreStages - 1 : slot - 1);
         cp_async_commit();
         e_issue += cols;
         ++r_issue;
         cp_async_wait<kPreStages - 1>();
         const char* base = stage + slot * kRowBytes;
-        slot = slot + 1 == kPreStages ? 0 : slot + 1;
         Raw8<T> g_raw;
         g_raw.from_shared(base, lane);
         const uint32_t wv = *reinterpret_cast<const uint32_t*>(base + NV * 512 + lane * 4);
@@ -398,12 +402,20 @@ __device__ __forceinline__ void pre_panel(const DevTensor& t, int64_t li, const 
             }
         }
         rmax = __reduce_max_sync(kFull, rmax);
-        if (lane == 0) {
-            atomic_max_nonneg(t.vrow_new + r, rmax);
-            if (rmax >= 0x7f800000u) atomicOr(status, QF_STATUS_NONFINITE);
-        }
+        const bool mine = (k_row & 31) == lane;
+        keep_lo = mine && k_row < 32 ? rmax : keep_lo;
+        keep_hi = mine && k_row >= 32 ? rmax : keep_hi;
+    };
+    int r = r0;
+    for (; r + kPreStages <= r1; r += kPreStages) {  // whole turns of the ring: slots are constants
+#pragma unroll
+        for (int i = 0; i < kPreStages; ++i) body(r + i, i);
     }
+    for (int i = 0; r < r1; ++r, ++i) body(r, i);    // fewer rows than one turn are left: the ring is at slot 0
     cp_async_wait<0>();
+    if (r0 + lane < r1) atomic_max_nonneg(t.vrow_new + r0 + lane, keep_lo);
+    if (r0 + 32 + lane < r1) atomic_max_nonneg(t.vrow_new + r0 + 32 + lane, keep_hi);
+    if (__any_sync(kFull, max(keep_lo, keep_hi) >= 0x7f800000u) && lane == 0) atomicOr(status, QF_STATUS_NONFINITE);
 #pragma unroll
     for (int k = 0; k < 8; ++k) atomic_max_nonneg(t.vcol_new + j0 + k, cmax[k]);
 }
@@ -588,8 +600,8 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
             const f2 nsv = mk2(fmaxf(nrow, ncn.x), fmaxf(nrow, ncn.y));
             const f2 rv = mk2(fmaxf(rrow, rcn.x), fmaxf(rrow, rcn.y));
             const f2 y = fma2(div2_prepared(v, rv, nsv), bc2(16.0f), bc2(-1.5f));
-            wq += code_from_y(y.x) << (8 * j);
-            wq += code_from_y(y.y) << (8 * j + 4);
+            wq += code_from_y<false>(y.x) << (8 * j);
+            wq += code_from_y<false>(y.y) << (8 * j + 4);
         }
         Elem<T>::store8(t.p, e, p);
         if (PUSH) push_store8<T>(t.p, e, p, push);
@@ -819,8 +831,8 @@ __device__ __forceinline__ void main_flat_run_fast(const DevTensor& t, int64_t w
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const f2 y = fma2(div2_prepared(v[j], r2, ns2), bc2(16.0f), bc2(-1.5f));
-            wq += code_from_y(y.x) << (8 * j);
-            wq += code_from_y(y.y) << (8 * j + 4);
+            wq += code_from_y<false>(y.x) << (8 * j);
+            wq += code_from_y<false>(y.y) << (8 * j + 4);
         }
     } else {
         wq = quantize8_pairs_exact(v[0], v[1], v[2], v[3], vs_new, s.t.mv);

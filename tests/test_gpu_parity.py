@@ -144,6 +144,24 @@ def test_multi_tensor_step_free_running_bit_exact(split):
     assert stepper.status() == 0
 
 
+def test_workspace_may_be_recycled_between_calls():
+    """Identical descriptors on consecutive calls, and the workspace memory rewritten in between (what an allocator
+    does when it hands a freed address out again, zero-filled): the step must not work from a stale table."""
+    gen, params, ostates, gparams, gstates = _make_problem(RAGGED[:8])
+    stepper = AbiStepper(gparams, gstates, **HP)
+    gbuf = [torch.empty_like(p) for p in gparams]
+    for step in range(3):
+        grads = [make_grad(p.shape, p.dtype, gen=gen) for p in params]
+        for p, g, st in zip(params, grads, ostates):
+            CO.step_tensor(p, g, st, *_hp_args())
+        for b, g in zip(gbuf, grads):
+            b.copy_(g)
+        stepper.step(gbuf)
+        torch.cuda.synchronize()
+        stepper.ws.zero_()
+        _assert_same(params, ostates, gparams, gstates, f"step {step + 1}")
+
+
 def test_multi_tensor_step_teacher_forced():
     """Each step starts from the oracle's state, so a mismatch cannot hide behind an earlier one."""
     gen, params, ostates, gparams, gstates = _make_problem(RAGGED, seed=1)
