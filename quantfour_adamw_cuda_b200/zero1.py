@@ -35,7 +35,8 @@ import torch.distributed as dist
 from . import _lib
 from .optimizer import BLOCK, DEFAULT_THRESHOLD, make_hyper
 
-__all__ = ["ShardedFourBitAdamW", "FlatLayout", "flat_layout", "rank_records", "Record", "CudaBackend"]
+__all__ = ["ShardedFourBitAdamW", "FlatLayout", "flat_layout", "rank_records", "Record", "CudaBackend",
+           "assemble_full_state"]
 
 FP32, BLOCKQ, RANK1 = _lib.QF_KIND_FP32, _lib.QF_KIND_BLOCK, _lib.QF_KIND_RANK1
 
@@ -143,6 +144,61 @@ class RecordState:
     row_rcp: Optional[torch.Tensor] = None
     col_rcp: Optional[torch.Tensor] = None
     g: Optional[torch.Tensor] = None        # set per step: flat view of the gradient of the piece
+
+
+def assemble_full_state(pieces: Sequence[Dict[str, Any]], shapes: Sequence[Tuple[int, ...]], step: int,
+                        group: Dict[str, Any], threshold: int = DEFAULT_THRESHOLD) -> Dict[str, Any]:
+    """Join the pieces of all ranks (ShardedFourBitAdamW.pieces) into a state dict with FourBitAdamW's layout
+    (state keys step / exp_avg / exp_avg_sq / momentum_qstate / variance_qstate, fused_quantfour.py:61-70,
+    :110-128): pieces start on 128-element boundaries, so codes join on byte boundaries and scales on blocks."""
+    state: Dict[int, Dict[str, Any]] = {}
+    for t, shape in enumerate(shapes):
+        n = math.prod(shape) if shape else 1
+        kind = tensor_kind(tuple(shape), n, threshold)
+        q = kind != FP32
+        f: Dict[str, Any] = {"step": torch.tensor(float(step)),
+                             "momentum_qstate": {"enable": q, "overhead": {}, "qmap": None},
+                             "variance_qstate": {"enable": q, "overhead": {}, "qmap": None}}
+        mine = [e for e in pieces if e["tensor"] == t]
+        covered = sorted((e["a"], e["b"]) for e in mine)
+        if not covered or covered[0][0] != 0 or covered[-1][1] != n or any(x[1] != y[0] for x, y in zip(covered, covered[1:])):
+            raise ValueError(f"the pieces of tensor {t} do not tile it: {covered}")
+        if kind == FP32:
+            m, v = torch.zeros(n), torch.zeros(n)
+            for e in mine:
+                m[e["a"]:e["b"]] = e["m"]
+                v[e["a"]:e["b"]] = e["v"]
+            f["exp_avg"], f["exp_avg_sq"] = m.view(shape), v.view(shape)
+            state[t] = f
+            continue
+        nb, nblk = (n + 1) // 2, (n + BLOCK - 1) // BLOCK
+        m, v = torch.zeros(nb, dtype=torch.int8), torch.zeros(nb, dtype=torch.int8)
+        ms = torch.zeros(nblk)
+        vs = torch.zeros(nblk) if kind == BLOCKQ else None
+        rows = cols = None
+        if kind == RANK1:
+            rows, cols = torch.zeros(shape[0], 1), torch.zeros(1, shape[1])
+        for e in mine:
+            b0, b1, k0, k1 = e["a"] // 2, (e["b"] + 1) // 2, e["a"] // BLOCK, (e["b"] + BLOCK - 1) // BLOCK
+            m[b0:b1], v[b0:b1], ms[k0:k1] = e["m"], e["v"], e["m_scale"]
+            if kind == BLOCKQ:
+                vs[k0:k1] = e["v_scale"]
+            else:
+                lo, hi, vals = e["rows"]
+                rows[lo:hi, 0] = vals
+                cols[0] = e["cols"]
+        f["exp_avg"], f["exp_avg_sq"] = m, v
+        f["momentum_qstate"]["overhead"]["max1"] = ms
+        vo = f["variance_qstate"]["overhead"]
+        vo["dim"] = len(shape)
+        if kind == RANK1:
+            vo["max_dims"], vo["max1"] = [rows, cols], None
+        else:
+            vo["max1"] = vs
+        state[t] = f
+    pg = {k: v for k, v in group.items() if k != "params"}
+    pg["params"] = list(range(len(shapes)))
+    return {"state": state, "param_groups": [pg]}
 
 
 class CudaBackend:
@@ -266,7 +322,7 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
         self._build_state()
         self.peer_deltas: List[int] = []
         self._peer_bases: List[int] = []
-        self.comm = "nccl"
+        self.comm = self._comm_selected = "nccl"
         if comm != "nccl" and self.sharded and self.world > 1 and self.flat.is_cuda:
             self._setup_p2p(required=comm == "p2p")
 
@@ -357,7 +413,7 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
         ok = torch.tensor([0.0 if err else 1.0], device=dev)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
         if ok.item() == 1.0:
-            self.comm = "p2p"
+            self.comm = self._comm_selected = "p2p"
             return
         self.close()
         if required:
@@ -371,6 +427,11 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
             except Exception:  # noqa: BLE001 - shutting down
                 pass
         self._peer_bases, self.peer_deltas, self.comm = [], [], "nccl"
+
+    @property
+    def comm_selected(self) -> str:
+        """The way parameters were delivered before any close(): "p2p" or "nccl"."""
+        return self._comm_selected
 
     # ---- step -------------------------------------------------------------------------------------
 
@@ -436,6 +497,79 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
         else:  # CPU process groups (tests): list form, the input must not alias the outputs
             chunks = [self.flat[r * self.layout.shard:(r + 1) * self.layout.shard] for r in range(self.world)]
             dist.all_gather(chunks, self.flat[lo:hi].clone(), group=self.group)
+
+    # ---- conversion between the sharded state and the per-parameter layout of FourBitAdamW --------------
+
+    def pieces(self) -> List[Dict[str, Any]]:
+        """This rank's records with their state on the CPU, in the form `assemble_full_state` takes."""
+        out = []
+        for st in self.states:
+            r = st.rec
+            e: Dict[str, Any] = {"tensor": r.tensor, "kind": r.kind, "a": r.a, "b": r.b,
+                                 "m": st.m.detach().cpu().clone(), "v": st.v.detach().cpu().clone()}
+            if r.kind != FP32:
+                e["m_scale"] = st.m_scale.detach().cpu().clone()
+            if r.kind == BLOCKQ:
+                e["v_scale"] = st.v_scale.detach().cpu().clone()
+            if r.kind == RANK1:
+                R, Cc = self.layout.shapes[r.tensor]
+                old = self.rank1_buf[r.tensor][0].detach().cpu()
+                # the rows this piece touches are current on this rank; so are all columns
+                lo, hi = r.a // Cc, (r.b - 1) // Cc + 1
+                e["rows"] = (lo, hi, old[lo:hi].clone())
+                e["cols"] = old[_round_up(R, 4):_round_up(R, 4) + Cc].clone()
+            out.append(e)
+        return out
+
+    def full_state_dict(self) -> Dict[str, Any]:
+        """The state of all ranks as one state dict in FourBitAdamW's layout (every rank returns it; a collective
+        when the optimizer runs under a process group).  FourBitAdamW.load_state_dict reads it, and so does
+        load_full_state_dict of a ShardedFourBitAdamW of any world size over the same parameter list."""
+        mine = self.pieces()
+        if self.sharded and self.world > 1:
+            everyone: List[Any] = [None] * self.world
+            dist.all_gather_object(everyone, mine, group=self.group)
+            allp = [e for part in everyone for e in part]
+        elif self.world > 1:
+            raise RuntimeError("without a process group, collect pieces() of every instance and call assemble_full_state")
+        else:
+            allp = mine
+        return assemble_full_state(allp, self.layout.shapes, self.step_count, self.param_groups[0], self.param_quant_threshold)
+
+    def load_full_state_dict(self, sd: Dict[str, Any]) -> None:
+        """Take this rank's part of a state dict in FourBitAdamW's layout (written by FourBitAdamW.state_dict or by
+        full_state_dict under any world size).  All parameters must be at the same step."""
+        ids = list(sd["param_groups"][0]["params"])
+        if len(sd["param_groups"]) != 1 or len(ids) != len(self.params):
+            raise ValueError("the state dict must hold one parameter group over the same parameter list")
+        full = [sd["state"][i] for i in ids]
+        steps = {float(f["step"]) for f in full}
+        if len(steps) != 1:
+            raise ValueError("ShardedFourBitAdamW keeps one step count; the state dict holds parameters at different steps")
+        self.step_count = int(steps.pop())
+        self.param_groups[0].update({k: v for k, v in sd["param_groups"][0].items() if k != "params"})
+        lay = self.layout
+        with torch.no_grad():
+            for t, f in enumerate(full):
+                kind = tensor_kind(lay.shapes[t], lay.numels[t], self.param_quant_threshold)
+                if kind == RANK1 and t in self.rank1_buf:
+                    R, Cc = lay.shapes[t]
+                    row, col = f["variance_qstate"]["overhead"]["max_dims"]
+                    old = self.rank1_buf[t][0]
+                    old[:R].copy_(row.reshape(-1))
+                    old[_round_up(R, 4):_round_up(R, 4) + Cc].copy_(col.reshape(-1))
+            for st in self.states:
+                r, f = st.rec, full[st.rec.tensor]
+                if r.kind == FP32:
+                    st.m.copy_(f["exp_avg"].reshape(-1)[r.a:r.b])
+                    st.v.copy_(f["exp_avg_sq"].reshape(-1)[r.a:r.b])
+                    continue
+                b0, b1, k0, k1 = r.a // 2, (r.b + 1) // 2, r.a // BLOCK, (r.b + BLOCK - 1) // BLOCK
+                st.m.copy_(f["exp_avg"][b0:b1])
+                st.v.copy_(f["exp_avg_sq"][b0:b1])
+                st.m_scale.copy_(f["momentum_qstate"]["overhead"]["max1"][k0:k1])
+                if r.kind == BLOCKQ:
+                    st.v_scale.copy_(f["variance_qstate"]["overhead"]["max1"][k0:k1])
 
     # ---- checkpoint ---------------------------------------------------------------------------------
 

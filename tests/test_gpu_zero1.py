@@ -115,3 +115,57 @@ def test_peer_export_reports_offset():
     big = torch.zeros(1 << 22, dtype=torch.uint8, device="cuda")
     handle, off = CudaBackend().export_buffer(big[4096:])
     assert len(handle) == 64 and off >= 4096 and (off - 4096) % 512 == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_state_moves_between_sharded_and_unsharded_optimizers(dtype):
+    """Three emulated ranks -> one state dict in the unsharded layout -> FourBitAdamW -> back into a sharded
+    optimizer of two ranks; the parameters follow the oracle through all three stages."""
+    from quantfour_adamw_cuda_b200 import FourBitAdamW
+    from quantfour_adamw_cuda_b200.zero1 import assemble_full_state
+    init, grads, want = _oracle_run(dtype, 6, 3)
+
+    def emulated(world, start):
+        out = []
+        for r in range(world):
+            params = [torch.nn.Parameter(p.clone().cuda()) for p in start]
+            out.append((params, ShardedFourBitAdamW(params, lr=1e-3, rank=r, world=world)))
+        return out
+
+    def emulated_step(ranks, gs):
+        shard = ranks[0][1].layout.shard
+        for params, opt in ranks:
+            for p, g in zip(params, gs):
+                p.grad = g.cuda()
+            opt.step_pre()
+        if ranks[0][1].shared_new.numel():
+            combined = torch.stack([opt.shared_new for _, opt in ranks]).max(dim=0).values
+            for _, opt in ranks:
+                opt.shared_new.copy_(combined)
+        for _, opt in ranks:
+            opt.step_main()
+        for r, (_, src) in enumerate(ranks):
+            for _, dst in ranks:
+                dst.flat[r * shard:(r + 1) * shard].copy_(src.flat[r * shard:(r + 1) * shard])
+
+    ranks = emulated(3, init)
+    for gs in grads[:2]:
+        emulated_step(ranks, gs)
+    opt0 = ranks[0][1]
+    full = assemble_full_state([e for _, o in ranks for e in o.pieces()], opt0.layout.shapes, opt0.step_count, opt0.param_groups[0])
+
+    params = [torch.nn.Parameter(p.detach().clone()) for p in ranks[0][0]]
+    plain = FourBitAdamW(params, lr=1e-3)
+    plain.load_state_dict(full)
+    for gs in grads[2:4]:
+        for p, g in zip(params, gs):
+            p.grad = g.cuda()
+        plain.step()
+
+    ranks2 = emulated(2, [p.detach().cpu() for p in params])
+    for _, opt in ranks2:
+        opt.load_full_state_dict(plain.state_dict())
+    for gs in grads[4:]:
+        emulated_step(ranks2, gs)
+    for i, (p, w) in enumerate(zip(ranks2[1][0], want)):
+        assert torch.equal(p.detach().cpu(), w), f"tensor {i} {SHAPES[i]} differs in {(p.detach().cpu() != w).sum()} places"
