@@ -210,6 +210,12 @@ def single_gpu(args):
         set_grads(i)
         opt.step()
     torch.cuda.synchronize(dev)
+    if args.start_step:
+        for st in opt.state.values():
+            st["step"].fill_(float(args.start_step))
+        set_grads(0)
+        opt.step()      # the optimizer notices the rewritten counters and rebuilds its per-step constants
+        torch.cuda.synchronize(dev)
 
     # ---- timed region: exactly K steps, device time -----------------------------------------------
     sampler = ClockSampler(dev.index)
@@ -284,6 +290,7 @@ def single_gpu(args):
         "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload, "tensors": len(shapes), "params": n_params, "param_dtype": "bf16",
+                   "start_step": args.start_step,
                    "state": "4-bit m (block-128) + 4-bit v (rank-1 / block-128), fp32 for numel <= 4096",
                    "l2": "inputs (%.1f GB per step) are far larger than L2" % (alg_bytes / 1e9),
                    "ms_per_step_min": min(per_step), "ms_per_step_max": max(per_step)},
@@ -354,6 +361,9 @@ def main():
     ap.add_argument("--workload", default=None, choices=[None, *S.WORKLOADS, "quantize"])
     ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "p2p"],
                     help="N>1: how the updated parameters reach the other ranks (peer stores from the update kernel, or an all-gather)")
+    ap.add_argument("--start-step", type=int, default=0,
+                    help="N=1: set every step counter to this value after the warm-up (>= 20000 shows the late-training "
+                         "regime where sqrt(1 - beta2^t) has rounded to 1)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

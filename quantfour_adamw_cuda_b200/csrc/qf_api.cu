@@ -239,15 +239,24 @@ int launch_pre(const Plan& pl, const qf::HyperPack& hp, cudaStream_t stream) {
     return QF_OK;
 }
 
+template <bool PUSH, bool BC1>
+int launch_main_panel(const Plan& pl, const qf::HyperPack& hp, const qf::PushPack& pp, cudaStream_t stream) {
+    const int dyn = qf::main_dyn_smem(pl.any_f32_panel);
+    const int ring = qf::kStages * (pl.any_f32_panel ? qf::kRowBytesF32 : qf::kRowBytesBf16);
+    QF_CUDA(cudaFuncSetAttribute(qf::step_main_kernel<true, PUSH, BC1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 qf::main_dyn_smem(true)));
+    qf::step_main_kernel<true, PUSH, BC1><<<persistent_grid(pl.items[kMainPanel], QF_MAIN_MIN_CTAS), qf::kThreads, dyn, stream>>>(
+        pl.d_tensors, pl.d_base[kMainPanel], pl.n, hp, ring, pl.d_status, pp);
+    return QF_OK;
+}
+
+// bc_one: every hyper-parameter set of the call has bc2s == 1 exactly (late in a run): the panel kernel then
+// runs the variant without the division by it.
 template <bool PUSH>
-int launch_main_kernels(const Plan& pl, const qf::HyperPack& hp, const qf::PushPack& pp, cudaStream_t stream) {
+int launch_main_kernels(const Plan& pl, const qf::HyperPack& hp, const qf::PushPack& pp, bool bc_one, cudaStream_t stream) {
     if (pl.items[kMainPanel]) {
-        const int dyn = qf::main_dyn_smem(pl.any_f32_panel);
-        const int ring = qf::kStages * (pl.any_f32_panel ? qf::kRowBytesF32 : qf::kRowBytesBf16);
-        QF_CUDA(cudaFuncSetAttribute(qf::step_main_kernel<true, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     qf::main_dyn_smem(true)));
-        qf::step_main_kernel<true, PUSH><<<persistent_grid(pl.items[kMainPanel], QF_MAIN_MIN_CTAS), qf::kThreads, dyn, stream>>>(
-            pl.d_tensors, pl.d_base[kMainPanel], pl.n, hp, ring, pl.d_status, pp);
+        if (int rc = bc_one ? launch_main_panel<PUSH, true>(pl, hp, pp, stream) : launch_main_panel<PUSH, false>(pl, hp, pp, stream))
+            return rc;
     }
     if (pl.items[kMainFlat])
         qf::step_main_kernel<false, PUSH><<<persistent_grid(pl.items[kMainFlat], QF_MAIN_MIN_CTAS), qf::kThreads, 0, stream>>>(
@@ -256,15 +265,17 @@ int launch_main_kernels(const Plan& pl, const qf::HyperPack& hp, const qf::PushP
 }
 
 // `push`: null, or the peer copies of the parameter buffer the kernels also store into.
-int launch_main(const Plan& pl, const qf::HyperPack& hp, cudaStream_t stream, const qf::PushPack* push = nullptr) {
+int launch_main(const Plan& pl, const qf::HyperPack& hp, int n_hypers, cudaStream_t stream, const qf::PushPack* push = nullptr) {
     if (pl.n == 0) return QF_OK;
     if (pl.n_rank1) roll(pl, qf::kRollRecip, stream);
+    bool bc_one = true;
+    for (int k = 0; k < n_hypers; ++k) bc_one = bc_one && hp.h[k].fast && hp.h[k].h.bc2s == 1.0f;
     if (push && push->n > 0) {
-        if (int rc = launch_main_kernels<true>(pl, hp, *push, stream)) return rc;
+        if (int rc = launch_main_kernels<true>(pl, hp, *push, bc_one, stream)) return rc;
     } else {
         qf::PushPack none;
         memset(&none, 0, sizeof none);
-        if (int rc = launch_main_kernels<false>(pl, hp, none, stream)) return rc;
+        if (int rc = launch_main_kernels<false>(pl, hp, none, bc_one, stream)) return rc;
     }
     if (pl.n_rank1) roll(pl, qf::kRollCommit, stream);
     QF_CUDA(cudaGetLastError());
@@ -303,7 +314,7 @@ int step_common(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers,
     if (pre)
         if (int rc = launch_pre(pl, hp, st)) return rc;
     if (main_)
-        if (int rc = launch_main(pl, hp, st, push)) return rc;
+        if (int rc = launch_main(pl, hp, n_hypers, st, push)) return rc;
     return QF_OK;
 }
 
@@ -716,7 +727,7 @@ int qf_step_rank1_noalloc(void* p, const void* g, void* m_codes, void* v_codes, 
     memset(&hp, 0, sizeof hp);
     hp.h[0] = widen_hyper(*hyper);
     if (int rc = launch_pre(pl, hp, st)) return rc;   // clears the new maxima first: the array keeps the last call's
-    return launch_main(pl, hp, st);
+    return launch_main(pl, hp, 1, st);
 }
 
 }  // extern "C"

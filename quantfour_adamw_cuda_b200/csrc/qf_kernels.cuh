@@ -241,7 +241,9 @@ __device__ __forceinline__ Hyper2 widen(const HyperDev& hd) {
 // The AdamW update of two elements; same roundings as adamw_elem.  V_FLOOR: the caller guarantees that the
 // old second moment is at least 2^-94 (a stored scale of at least 2^-90 times the smallest map value), so
 // the new one cannot fall below the range of the unchecked square root.
-template <bool V_FLOOR = false>
+// BC1: sqrt(1 - beta2^t) has rounded to exactly 1 (from about step 17 000 on with beta2 = 0.999, i.e. for most
+// of a long run), so the division by it is the identity and is left out.
+template <bool V_FLOOR = false, bool BC1 = false>
 __device__ __forceinline__ void adamw_pair(f2& p, f2 g, f2& m, f2& v, const Hyper2& h) {
     // p * decay as a fused multiply-add with a zero addend: same value, but unlike a packed multiply it
     // cannot be contracted with the add that consumes it further down (see qf_math.cuh).
@@ -249,7 +251,7 @@ __device__ __forceinline__ void adamw_pair(f2& p, f2 g, f2& m, f2& v, const Hype
     m = fma2(h.w1, fma2(m, bc2(-1.0f), g), m);            // m + w1 * (g - m)
     v = fma2(mul2(h.w2, g), g, mul2(h.beta2, v));          // beta2 * v + (w2 * g) * g
     const f2 s = sqrt2<!V_FLOOR>(v);
-    const f2 den = add2(div2_prepared(s, h.rb, h.nb), h.eps);
+    const f2 den = add2(BC1 ? s : div2_prepared(s, h.rb, h.nb), h.eps);
     p = add2(p1, div2(mul2(h.nstep, m), den));
 }
 __device__ __forceinline__ f2 v_update2(f2 g, f2 v_old, const Hyper2& h) {
@@ -476,7 +478,7 @@ constexpr int kColBytes = 3 * 4 * 32 * 8;              // per warp: old / new / 
 // L1 to the CTA, which the measurements reward.
 constexpr int main_dyn_smem(bool any_f32) { return kWarpsPerCta * (kStages * (any_f32 ? kRowBytesF32 : kRowBytesBf16) + kColBytes); }
 
-template <typename T, bool PUSH>
+template <typename T, bool PUSH, bool BC1>
 __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, const HyperDev& hd, const Smem& s,
                                            char* stage, int ring_bytes, uint32_t* status, const PushPack* push) {
     const DevTensor t = *tp;
@@ -593,7 +595,7 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
                 rcn = (j & 1) ? mk2(c.z, c.w) : mk2(c.x, c.y);
             }
             f2 v = mul2(pair_lookup(s.qv2, wv, j), mk2(fminf(row_old, co.x), fminf(row_old, co.y)));
-            adamw_pair<true>(pp, mk2(g[2 * j], g[2 * j + 1]), m[j], v, h2);
+            adamw_pair<true, BC1>(pp, mk2(g[2 * j], g[2 * j + 1]), m[j], v, h2);
             p[2 * j] = pp.x;
             p[2 * j + 1] = pp.y;
             // requantize v: scale = min(row', col') -> -scale = max(-row', -col'), 1/scale = max(1/row', 1/col')
@@ -916,7 +918,8 @@ __device__ __forceinline__ void main_flat_dispatch(const DevTensor* tp, int64_t 
 #define QF_MAIN_MIN_CTAS 2
 #endif
 // PUSH: the launch also stores every updated parameter vector into the peers' buffers named by `pp`.
-template <bool PANEL, bool PUSH>
+// BC1 (panel mapping only): every hyper-parameter set of the launch has bc2s == 1.
+template <bool PANEL, bool PUSH, bool BC1 = false>
 __global__ void __launch_bounds__(kThreads, QF_MAIN_MIN_CTAS)
 step_main_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict__ base, int n,
                  const __grid_constant__ HyperPack hp, int ring_bytes, uint32_t* status,
@@ -934,9 +937,9 @@ step_main_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restric
         const HyperDev& h = hp.h[tp->hyper];  // hp is a grid constant: its address is usable as it is
         if (PANEL) {
             if (tp->dtype == QF_BF16)
-                main_panel<__nv_bfloat16, PUSH>(tp, li, h, s, stage, ring_bytes, status, push);
+                main_panel<__nv_bfloat16, PUSH, BC1>(tp, li, h, s, stage, ring_bytes, status, push);
             else
-                main_panel<float, PUSH>(tp, li, h, s, stage, ring_bytes, status, push);
+                main_panel<float, PUSH, BC1>(tp, li, h, s, stage, ring_bytes, status, push);
         } else {
             if (tp->dtype == QF_BF16)
                 main_flat_dispatch<__nv_bfloat16>(tp, li, h, s, status, push);

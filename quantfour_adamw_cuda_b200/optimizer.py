@@ -307,7 +307,7 @@ class FourBitAdamW(torch.optim.Optimizer):
         classes = [None] * len(hyper_index)
         for p, _, st, hi in entries:
             if classes[hi] is None:
-                classes[hi] = [group_of[id(p)], float(st["step"])]
+                classes[hi] = [group_of[id(p)], float(st["step"]), st["step"]]
         self._fast = {
             "dev": dev, "plan": self._plans[(dev.index, 0)], "checks": [(p, p.data_ptr(), g.data_ptr()) for p, g, _, _ in entries],
             "absent": [p for g in self.param_groups for p in g["params"] if id(p) not in seen],
@@ -332,6 +332,9 @@ class FourBitAdamW(torch.optim.Optimizer):
                 moved.append((i, g))
         for p in f["absent"]:
             if p.grad is not None:
+                return False
+        for c in f["classes"]:
+            if float(c[2]) != c[1]:      # somebody rewrote a step counter: rebuild the classes
                 return False
         for i, g in moved:
             plan.descs[i].g = g.data_ptr()

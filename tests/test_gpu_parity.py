@@ -162,6 +162,22 @@ def test_workspace_may_be_recycled_between_calls():
         _assert_same(params, ostates, gparams, gstates, f"step {step + 1}")
 
 
+def test_late_steps_where_the_bias_correction_has_rounded_to_one():
+    """From about step 17 000 on (beta2 = 0.999) sqrt(1 - beta2^t) is exactly 1.0f and the library runs the kernel
+    variant without that division: same bits as the oracle, which still divides."""
+    gen, params, ostates, gparams, gstates = _make_problem(RAGGED)
+    for st, gs in zip(ostates, gstates):
+        st.step = gs.step = 30000
+    assert np.float32(TO.Hyper.make(1e-3, 0.9, 0.999, 1e-8, 0.01, 30001).bc2s) == np.float32(1.0)
+    stepper = AbiStepper(gparams, gstates, **HP)
+    for step in range(4):
+        grads = [make_grad(p.shape, p.dtype, gen=gen) for p in params]
+        for p, g, st in zip(params, grads, ostates):
+            CO.step_tensor(p, g, st, *_hp_args())
+        stepper.step([g.to(DEV) for g in grads])
+        _assert_same(params, ostates, gparams, gstates, f"step {30001 + step}")
+
+
 def test_multi_tensor_step_teacher_forced():
     """Each step starts from the oracle's state, so a mismatch cannot hide behind an earlier one."""
     gen, params, ostates, gparams, gstates = _make_problem(RAGGED, seed=1)
