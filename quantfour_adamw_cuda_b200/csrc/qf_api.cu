@@ -210,12 +210,12 @@ int sm_count() {
     }
     return cached[dev];
 }
-unsigned persistent_grid(int64_t items, int per_sm) {
-    const int64_t ctas = (items + qf::kWarpsPerCta - 1) / qf::kWarpsPerCta;
 #ifndef QF_GRID_WAVES
 #define QF_GRID_WAVES 16
 #endif
-    const int64_t cap = static_cast<int64_t>(sm_count()) * per_sm * QF_GRID_WAVES;
+unsigned persistent_grid(int64_t items, int per_sm, int waves = QF_GRID_WAVES) {
+    const int64_t ctas = (items + qf::kWarpsPerCta - 1) / qf::kWarpsPerCta;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * per_sm * waves;
     return static_cast<unsigned>(ctas < cap ? ctas : cap);
 }
 
@@ -545,7 +545,7 @@ int qf_quantize_block(const float* x, int64_t numel, int map, uint8_t* codes, fl
     if (!scales) return fail(QF_ERR_BAD_ARG, "scales is null");
     QF_CUDA(cudaSetDevice(device));
     const int vec = aligned(x, 16) && aligned(codes, 4);
-    qf::quantize_block_kernel<<<flat_grid(numel), qf::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(x, numel, map, codes,
+    qf::quantize_block_kernel<<<persistent_grid(flat_items(numel), 8, 2), qf::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(x, numel, map, codes,
                                                                                                       scales, vec);
     QF_CUDA(cudaGetLastError());
     return QF_OK;
@@ -580,8 +580,9 @@ int qf_quantize_rank1(const float* v, int64_t rows, int64_t cols, uint8_t* codes
     const int vec = aligned(v, 16) && aligned(codes, 4);
     const int panel = vec && cols % qf::kPanelCols == 0;
     const int64_t items = panel ? (rows + qf::kRowsPerItem - 1) / qf::kRowsPerItem * (cols / qf::kPanelCols) : flat_items(numel);
+    const int64_t max_items = panel ? (rows + qf::kPreRowsPerItem - 1) / qf::kPreRowsPerItem * (cols / qf::kPanelCols) : items;
     unsigned grid;
-    if (int rc = grid_for(items, &grid)) return rc;
+    if (int rc = grid_for(max_items, &grid)) return rc;
     qf::rank1_max_kernel<<<grid, qf::kThreads, 0, st>>>(v, static_cast<int>(rows), static_cast<int>(cols), row_max, col_max, panel);
     if (panel && aligned(col_max, 16))
         qf::rank1_codec_panel_kernel<true><<<persistent_grid(items, 8), qf::kThreads, 0, st>>>(v, codes, row_max, col_max, static_cast<int>(rows),

@@ -1007,15 +1007,28 @@ quantize_block_kernel(const float* __restrict__ x, int64_t numel, int map, uint8
     load_smem(s);
     const float* mid = map ? s.t.mv : s.t.mm;
     const int lane = threadIdx.x & 31;
-    const int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
-    const int64_t start = item * (kPanelCols * kRowsPerItem);
+    // warps stride over the items, so that a CTA fills its search table once for many items
+    const int64_t per_item = static_cast<int64_t>(kPanelCols) * kRowsPerItem;
+    const int64_t total = (numel + per_item - 1) / per_item, stride = static_cast<int64_t>(gridDim.x) * kWarpsPerCta;
+    for (int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5); item < total; item += stride) {
+    const int64_t start = item * per_item;
+    // the next run's input is requested before this run is worked on
+    auto fetch = [&](int64_t wbase, float (&dst)[8]) {
+        const int64_t e = wbase + lane * 8;
+        const int nv = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(8), numel - e)));
+        load8_masked<float>(reinterpret_cast<const char*>(x), e, nv, vec, dst);
+    };
+    float vn[8];
+    if (start < numel) fetch(start, vn);
     for (int it = 0; it < kRowsPerItem; ++it) {
         const int64_t wbase = start + static_cast<int64_t>(it) * kPanelCols;
         if (wbase >= numel) break;
         const int64_t e = wbase + lane * 8;
         const int nv = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(8), numel - e)));
         float v[8];
-        load8_masked<float>(reinterpret_cast<const char*>(x), e, nv, vec, v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = vn[k];
+        if (it + 1 < kRowsPerItem && wbase + kPanelCols < numel) fetch(wbase + kPanelCols, vn);
         const float sc = absmax8_bits_to_block(v);
         if (vec && wbase + kPanelCols <= numel && scale_safe(sc)) {  // full run: packed division, table search
             const f2 r2 = bc2(sc == 0.0f ? 0.0f : __frcp_rn(sc)), ns2 = bc2(-sc);
@@ -1033,6 +1046,7 @@ quantize_block_kernel(const float* __restrict__ x, int64_t numel, int map, uint8
         }
         if (nv && (lane & 15) == 0) scales[e >> 7] = sc;
     }
+    }
 }
 
 __global__ void __launch_bounds__(kThreads)
@@ -1044,16 +1058,32 @@ dequantize_block_kernel(const uint8_t* __restrict__ codes, const float* __restri
     const int lane = threadIdx.x & 31;
     const int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
     const int64_t start = item * (kPanelCols * kRowsPerItem);
-    for (int it = 0; it < kRowsPerItem; ++it) {
-        const int64_t e = start + static_cast<int64_t>(it) * kPanelCols + lane * 8;
+    // the code words and scales of four runs are requested together, then expanded and stored
+    for (int it0 = 0; it0 < kRowsPerItem; it0 += 4) {
+        uint32_t wv[4];
+        float scv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int64_t e = start + static_cast<int64_t>(it0 + i) * kPanelCols + lane * 8;
+            wv[i] = 0;
+            scv[i] = 0.0f;
+            if (e < numel) {
+                wv[i] = load_codes(codes, e, static_cast<int>(min(static_cast<int64_t>(8), numel - e)), vec);
+                scv[i] = __ldg(scales + (e >> 7));
+            }
+        }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int64_t e = start + static_cast<int64_t>(it0 + i) * kPanelCols + lane * 8;
         if (e >= numel) break;
         const int nv = static_cast<int>(min(static_cast<int64_t>(8), numel - e));
-        const uint32_t w = load_codes(codes, e, nv, vec);
-        const float sc = __ldg(scales + (e >> 7));
+        const uint32_t w = wv[i];
+        const float sc = scv[i];
         float v[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) v[k] = __fmul_rn(q[nib(w, k)], sc);
         store8_masked<float>(reinterpret_cast<char*>(out), e, nv, vec, v);
+    }
     }
 }
 
@@ -1067,25 +1097,31 @@ rank1_max_kernel(const float* __restrict__ v, int rows, int cols, float* __restr
     if (panel) {
         const int panels = cols / kPanelCols;
         const int band = static_cast<int>(item / panels);
-        const int r0 = band * kRowsPerItem;
+        const int r0 = band * kPreRowsPerItem;  // tall items: one column atomic per 64 rows
         if (r0 >= rows) return;
-        const int r1 = min(r0 + kRowsPerItem, rows);
+        const int r1 = min(r0 + kPreRowsPerItem, rows);
         const int j0 = static_cast<int>(item - static_cast<int64_t>(band) * panels) * kPanelCols + lane * 8;
         uint32_t cmax[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) cmax[k] = 0;
-        for (int r = r0; r < r1; ++r) {
-            float x[8];
-            load8f(v, static_cast<int64_t>(r) * cols + j0, x);
-            uint32_t rmax = 0;
+        // four rows are requested together (4 KB per warp in flight): this pass does almost no arithmetic and
+        // lives on memory-level parallelism.  Past the last row the last row is read again, which changes no maximum.
+        for (int rb = r0; rb < r1; rb += 4) {
+            float x[4][8];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const uint32_t b = absbits(x[k]);
-                rmax = max(rmax, b);
-                cmax[k] = max(cmax[k], b);
+            for (int i = 0; i < 4; ++i) load8f(v, static_cast<int64_t>(min(rb + i, r1 - 1)) * cols + j0, x[i]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint32_t rmax = 0;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const uint32_t b = absbits(x[i][k]);
+                    rmax = max(rmax, b);
+                    cmax[k] = max(cmax[k], b);
+                }
+                rmax = __reduce_max_sync(kFull, rmax);
+                if (lane == 0 && rb + i < r1) atomic_max_nonneg(row_max + rb + i, rmax);
             }
-            rmax = __reduce_max_sync(kFull, rmax);
-            if (lane == 0) atomic_max_nonneg(row_max + r, rmax);
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k) atomic_max_nonneg(col_max + j0 + k, cmax[k]);
@@ -1134,12 +1170,29 @@ rank1_codec_panel_kernel(const float* __restrict__ in, uint8_t* __restrict__ cod
 #pragma unroll
         for (int k = 0; k < 8; ++k) ok &= scale_safe(col[k]) && col[k] > 0.0f;
         const bool col_fast = __all_sync(kFull, ok);
+        // the next row's input is requested before this row is worked on: two rows per warp in flight
+        float xn[8];
+        uint32_t wn = 0;
+        float rown = __ldg(row_max + r0);
+        if (QUANT)
+            load8f(in, static_cast<int64_t>(r0) * cols + j0, xn);
+        else
+            wn = __ldg(reinterpret_cast<const uint32_t*>(codes + ((static_cast<int64_t>(r0) * cols + j0) >> 1)));
         for (int r = r0; r < r1; ++r) {
             const int64_t e = static_cast<int64_t>(r) * cols + j0;
-            const float row = __ldg(row_max + r);
+            const float row = rown;
+            float x[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) x[k] = xn[k];
+            const uint32_t wcur = wn;
+            if (r + 1 < r1) {
+                rown = __ldg(row_max + r + 1);
+                if (QUANT)
+                    load8f(in, e + cols, xn);
+                else
+                    wn = __ldg(reinterpret_cast<const uint32_t*>(codes + ((e + cols) >> 1)));
+            }
             if (QUANT) {
-                float x[8];
-                load8f(in, e, x);
                 uint32_t w = 0;
                 if (col_fast && scale_safe(row) && row > 0.0f) {  // warp-uniform
 #pragma unroll
@@ -1155,8 +1208,7 @@ rank1_codec_panel_kernel(const float* __restrict__ in, uint8_t* __restrict__ cod
                 }
                 *reinterpret_cast<uint32_t*>(codes + (e >> 1)) = w;
             } else {
-                const uint32_t w = *reinterpret_cast<const uint32_t*>(codes + (e >> 1));
-                float x[8];
+                const uint32_t w = wcur;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const f2 v = mul2(pair_lookup(s.qv2, w, j), mk2(fminf(row, col[2 * j]), fminf(row, col[2 * j + 1])));

@@ -26,6 +26,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import socket
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
@@ -393,14 +394,16 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
         self._token = torch.zeros(1, dtype=torch.float32, device=dev)
         err, mine = "", None
         try:
-            mine = self.backend.export_buffer(self.flat)
+            mine = self.backend.export_buffer(self.flat) + (socket.gethostname(),)
         except Exception as e:  # noqa: BLE001 - any failure means: no peer path
             err = f"{type(e).__name__}: {e}"
         everyone: List[Any] = [None] * self.world
         dist.all_gather_object(everyone, mine, group=self.group)
+        if not err and any(x is not None and x[2] != everyone[self.rank][2] for x in everyone):
+            err = "the ranks run on different hosts"     # a handle means nothing on another machine: do not try it
         if not err and all(x is not None for x in everyone) and self.world - 1 <= _lib.QF_MAX_PEERS:
             try:
-                for r, (handle, off) in enumerate(everyone):
+                for r, (handle, off, _) in enumerate(everyone):
                     if r == self.rank:
                         continue
                     base, addr = self.backend.open_buffer(handle, off, dev)
