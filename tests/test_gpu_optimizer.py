@@ -171,3 +171,33 @@ def test_cpu_parameters_and_bad_dtypes_fail_loudly():
     h.grad = torch.randn_like(h)
     with pytest.raises(TypeError):
         qf.FourBitAdamW([h]).step()
+
+
+def test_tensor_with_more_than_2_to_31_elements():
+    """64-bit element indexing: a 1-D tensor of 2^31 + 640 elements steps exactly like the same data cut into two
+    tensors at a block boundary (block-128 state is independent per block)."""
+    import quantfour_adamw_cuda_b200 as qf
+    free, _ = torch.cuda.mem_get_info()
+    if free < 40 * 2**30:
+        pytest.skip("needs about 30 GB of device memory")
+    n, cut = 2**31 + 640, 2**30
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    base = torch.empty(n, dtype=torch.bfloat16, device="cuda").normal_(0, 0.02, generator=gen)
+    whole = torch.nn.Parameter(base.clone())
+    halves = [torch.nn.Parameter(base[:cut].clone()), torch.nn.Parameter(base[cut:].clone())]
+    del base
+    o1, o2 = qf.FourBitAdamW([whole], lr=1e-3), qf.FourBitAdamW(halves, lr=1e-3)
+    for _ in range(2):
+        g = torch.empty(n, dtype=torch.bfloat16, device="cuda").normal_(0, 1e-3, generator=gen)
+        whole.grad = g
+        halves[0].grad, halves[1].grad = g[:cut], g[cut:]
+        o1.step()
+        o2.step()
+    assert torch.equal(whole.detach()[:cut], halves[0].detach()) and torch.equal(whole.detach()[cut:], halves[1].detach())
+    s1 = o1.state[whole]
+    for key in ("exp_avg", "exp_avg_sq"):
+        joined = torch.cat([o2.state[h][key] for h in halves])
+        assert torch.equal(s1[key], joined), key
+    joined = torch.cat([o2.state[h]["momentum_qstate"]["overhead"]["max1"] for h in halves])
+    assert torch.equal(s1["momentum_qstate"]["overhead"]["max1"], joined)
+    assert not o1.nonfinite_seen()
