@@ -4,13 +4,15 @@
 // load of bf16 parameters, one 32-bit word of codes), so a warp covers 256 consecutive elements = two
 // 128-element quantization blocks, and a block's abs-max is a 4-step shuffle among 16 lanes with no
 // shared memory and no CTA barrier.  A warp work item is
-//   * for rank-1 tensors whose column count is a multiple of 256 ("panel" mapping): kRowsPerItem rows
-//     of one 256-column panel.  A lane keeps the same 8 columns for the whole item, so everything that
-//     depends on the column only (old and new column maxima, their reciprocals) lives in registers, and
-//     the first pass reduces column maxima over the rows in registers before touching global memory;
-//   * otherwise ("flat" mapping): kRowsPerItem consecutive runs of 256 flattened elements.
+//   * for rank-1 tensors whose column count is a multiple of 256 ("panel" mapping): 64 rows of one
+//     256-column panel.  A lane keeps the same 8 columns for the whole item, so everything that depends on
+//     the column only (old and new column maxima, their reciprocals) is fetched once per item (registers in
+//     the first pass, the warp's slice of shared memory in the main pass), and the first pass reduces column
+//     maxima over the rows in registers before touching global memory;
+//   * otherwise ("flat" mapping): kRowsPerItem (16) consecutive runs of 256 flattened elements.
 // A multi-tensor launch numbers the work items of all tensors of one mapping consecutively; a warp finds
-// its tensor by binary search in the prefix-sum table.  CTAs hold 8 warps that take 8 consecutive items.
+// its tensor by binary search in the prefix-sum table.  The step kernels are persistent: CTAs of 8 warps,
+// every warp striding over the item list.
 //
 // Rank-1 second moments need the new row/column maxima of the whole tensor before any element can be
 // requantized, hence two passes: `pre` recomputes v from (g, old codes) and accumulates the maxima with
