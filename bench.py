@@ -364,6 +364,8 @@ def main():
     ap.add_argument("--start-step", type=int, default=0,
                     help="N=1: set every step counter to this value after the warm-up (>= 20000 shows the late-training "
                          "regime where sqrt(1 - beta2^t) has rounded to 1)")
+    ap.add_argument("--reduce-grads", action="store_true",
+                    help="N>1: the step starts with a reduce-scatter (mean) of per-rank gradients kept in a flat buffer")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

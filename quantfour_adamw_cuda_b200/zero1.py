@@ -279,13 +279,19 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
     """FourBitAdamW with ZeRO-1 style sharding of the 4-bit state over the ranks of `process_group`.
 
     Same constructor arguments as FourBitAdamW.  All parameters must share one dtype (float32 or bfloat16)
-    and one device, and every parameter must have a gradient at each step.  With `flatten=True` (default)
-    the parameters are moved into one flat buffer and become views of it.
+    and one device, and every parameter must have a gradient at each step.  The parameters are moved into
+    one flat buffer and become views of it.
+
+    `reduce_grads=True` adds the other half of ZeRO-1: the gradients live in a flat buffer of the same layout
+    (every `p.grad` is a view of it, so backward accumulates in place), the ranks hold different gradients,
+    and each step starts with a reduce-scatter that leaves the mean over the ranks of this rank's range where
+    the step reads it.  Without it (default) the caller has already made the gradients equal on all ranks.
     """
 
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, *, fused: Optional[bool] = False,
                  quant_threshold: int = DEFAULT_THRESHOLD, process_group=None, backend=None,
-                 rank: Optional[int] = None, world: Optional[int] = None, comm: str = "auto"):
+                 rank: Optional[int] = None, world: Optional[int] = None, comm: str = "auto",
+                 reduce_grads: bool = False):
         if not 0.0 < lr:
             raise ValueError(f"Invalid learning rate: {lr=}")
         if not 0.0 < eps:
@@ -321,6 +327,11 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
             raise ValueError(f"comm must be 'auto', 'nccl' or 'p2p', got {comm!r}")
         self._flatten()
         self._build_state()
+        self.reduce_grads = bool(reduce_grads)
+        self.flat_grad: Optional[torch.Tensor] = None
+        if self.reduce_grads:
+            self.flat_grad = torch.zeros_like(self.flat)
+            self._attach_grad_views()
         self.peer_deltas: List[int] = []
         self._peer_bases: List[int] = []
         self.comm = self._comm_selected = "nccl"
@@ -337,6 +348,39 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
                 view = self.flat[off:off + n].view(p.shape)
                 view.copy_(p)
                 p.data = view
+
+    def _attach_grad_views(self) -> None:
+        """Make every p.grad the parameter's view of the flat gradient buffer (copying a gradient that was
+        produced elsewhere, e.g. after zero_grad(set_to_none=True))."""
+        for p, off, n in zip(self.params, self.layout.offsets, self.layout.numels):
+            view = self.flat_grad[off:off + n].view(p.shape)
+            if p.grad is not None and p.grad.data_ptr() != view.data_ptr():
+                if p.grad.is_sparse:
+                    raise RuntimeError("QuantFour AdamW does not support sparse gradients")
+                view.copy_(p.grad)
+            p.grad = view
+
+    def zero_grad(self, set_to_none: bool = False) -> None:
+        if not self.reduce_grads:
+            return super().zero_grad(set_to_none=set_to_none)
+        self.flat_grad.zero_()          # the views stay attached: backward keeps accumulating in place
+        for p, off, n in zip(self.params, self.layout.offsets, self.layout.numels):
+            if p.grad is None or p.grad.data_ptr() != self.flat_grad[off:off + n].data_ptr():
+                p.grad = self.flat_grad[off:off + n].view(p.shape)
+
+    def _reduce_gradients(self) -> None:
+        """Mean of the ranks' gradients over this rank's range of the flat gradient buffer, in place."""
+        if any(p.grad is None for p in self.params):
+            raise RuntimeError("ShardedFourBitAdamW needs a gradient for every parameter at every step")
+        self._attach_grad_views()
+        if not (self.sharded and self.world > 1):
+            return
+        lo, hi = self.layout.range_of(self.rank)
+        if self.flat_grad.is_cuda:
+            dist.reduce_scatter_tensor(self.flat_grad[lo:hi], self.flat_grad, op=dist.ReduceOp.AVG, group=self.group)
+        else:  # CPU process groups (tests)
+            dist.all_reduce(self.flat_grad, op=dist.ReduceOp.SUM, group=self.group)
+            self.flat_grad.mul_(1.0 / self.world)
 
     def _build_state(self) -> None:
         dev = self.flat.device
@@ -444,6 +488,8 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
+        if self.reduce_grads:
+            self._reduce_gradients()
         self.step_pre()
         multi = self.sharded and self.world > 1
         if multi and self.shared_new.numel():

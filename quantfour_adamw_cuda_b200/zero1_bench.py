@@ -59,9 +59,16 @@ def run(args, hp) -> None:
     shapes = S.WORKLOADS[workload]()
     n_params, alg_bytes = S.numel(shapes), S.algorithmic_bytes(shapes)
     params, grads = bench.build_problem(shapes, dev, seed=0, grad_sets=1)   # same seed: replicated parameters
-    opt = ShardedFourBitAdamW(params, comm=getattr(args, "comm", None) or "auto", **hp)
-    for p, g in zip(params, grads[0]):
-        p.grad = g
+    reduce_grads = bool(getattr(args, "reduce_grads", False))
+    opt = ShardedFourBitAdamW(params, comm=getattr(args, "comm", None) or "auto", reduce_grads=reduce_grads, **hp)
+    if reduce_grads:     # the gradients live in the optimizer's flat buffer; every rank holds the same values here,
+        for p, g in zip(params, grads[0]):   # so their mean leaves them unchanged from step to step
+            p.grad.copy_(g)
+        grads = None
+        torch.cuda.empty_cache()
+    else:
+        for p, g in zip(params, grads[0]):
+            p.grad = g
     warm = max(3, args.warmup)
     for _ in range(warm):
         opt.step()
@@ -102,6 +109,17 @@ def run(args, hp) -> None:
         for k in range(3):
             parts[k] += e[k].elapsed_time(e[k + 1]) / reps
     parts = [_max_over_ranks(x, dev) for x in parts]
+    reduce_ms = None
+    if reduce_grads:
+        reduce_ms = 0.0
+        for _ in range(reps):
+            dist.barrier()
+            e[0].record()
+            opt._reduce_gradients()
+            e[1].record()
+            torch.cuda.synchronize(dev)
+            reduce_ms += e[0].elapsed_time(e[1]) / reps
+        reduce_ms = _max_over_ranks(reduce_ms, dev)
     push_ms = None
     if opt.comm == "p2p":   # the fused main pass: update + peer stores, closed by the small collective
         push_ms = 0.0
@@ -121,6 +139,8 @@ def run(args, hp) -> None:
     shard_elements, flat_total = opt.layout.shard, opt.layout.total
     # end to end: this rank's slices of the gradients arrive from pinned host memory every step
     e2e = None
+    if reduce_grads:
+        args.no_e2e = True    # the end-to-end leg feeds only this rank's slices, which is not what a reduce-scatter consumes
     if not args.no_e2e:
         host = [st.g.cpu().pin_memory() for st in opt.states]
         h2d = sum(t.numel() * t.element_size() for t in host)
@@ -170,13 +190,14 @@ def run(args, hp) -> None:
             "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": workload, "tensors": len(shapes), "params": n_params, "param_dtype": "bf16",
-                       "parallelism": f"zero1-dp{world}", "shard_elements": shard_elements, "comm": comm_used,
+                       "parallelism": f"zero1-dp{world}", "shard_elements": shard_elements, "comm": comm_used, "reduce_grads": reduce_grads,
                        "l2": "inputs (%.1f GB per rank and step) are far larger than L2" % (shard_bytes / 1e9)},
             "roofline": {"bound": "hbm", "achieved": shard_bytes / (compute_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": shard_bytes / (compute_ms * 1e-3) / 1e9 / peak, "traffic": None, "peak_kind": peak_kind,
                          "note": "per rank: algorithmic bytes of the rank's shard over the device time of its fused step "
                                  "(both halves incl. the max exchange), all-gather excluded",
-                         "parts_ms": {"pre+max_exchange": parts[0], "main": parts[1], "all_gather": parts[2]},
+                         "parts_ms": {"pre+max_exchange": parts[0], "main": parts[1], "all_gather": parts[2],
+                                      "grad_reduce_scatter": reduce_ms},
                          "all_gather": {"bytes_received_per_gpu": gather_bytes,
                                         "GBps_per_gpu": gather_bytes / (parts[2] * 1e-3) / 1e9 if parts[2] else None,
                                         "link_peak_GBps": 770.0},

@@ -47,6 +47,26 @@ for dtype in (torch.bfloat16, torch.float32):
             assert torch.equal(p.detach().cpu(), w), f"rank {rank} {comm} {dtype} tensor {i} {SHAPES[i]}"
     assert torch.equal(runs["p2p"][1].flat, runs["nccl"][1].flat)
     runs["p2p"][1].close()
+# the ranks hold different gradients; the step starts with the reduce-scatter (mean) of the flat gradient buffer
+for dtype in (torch.bfloat16, torch.float32):
+    gen = torch.Generator().manual_seed(9)
+    init = [(torch.randn(s, generator=gen) * 0.02).to(dtype) for s in SHAPES]
+    want = [p.clone() for p in init]
+    states = [TO.TensorState.zeros(s) for s in SHAPES]
+    params = [torch.nn.Parameter(p.to(dev)) for p in init]
+    opt = ShardedFourBitAdamW(params, lr=1e-3, reduce_grads=True)
+    for step in range(4):
+        opt.zero_grad()
+        for p, w, st in zip(params, want, states):
+            per_rank = [(torch.randn(w.shape, generator=gen) * 1e-3).to(dtype) for _ in range(2)]
+            mean = ((per_rank[0].float() + per_rank[1].float()) * 0.5).to(dtype)
+            CO.step_tensor(w, mean, st, *HP)
+            p.grad.add_(per_rank[rank].to(dev))
+        opt.step()
+    torch.cuda.synchronize(dev)
+    for i, (p, w) in enumerate(zip(params, want)):
+        assert torch.equal(p.detach().cpu(), w), f"rank {rank} reduce_grads {dtype} tensor {i} {SHAPES[i]}"
+    opt.close()
 dist.barrier()
 dist.destroy_process_group()
 print(f"rank {rank} ok")

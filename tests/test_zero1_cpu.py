@@ -231,3 +231,46 @@ def test_full_state_dict_loads_into_the_unsharded_optimizer():
         if a["variance_qstate"]["overhead"].get("max_dims") is not None:
             for x, y in zip(a["variance_qstate"]["overhead"]["max_dims"], b["variance_qstate"]["overhead"]["max_dims"]):
                 assert torch.equal(x, y) and y.dtype == torch.float32
+
+
+# ---- gradients reduced inside the step ---------------------------------------------------------------------------
+
+def _worker_reduce(rank, world, port, steps, out):
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from sharded_cpu_backend import CpuBackend
+    from quantfour_adamw_cuda_b200.zero1 import ShardedFourBitAdamW
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        gen = torch.Generator().manual_seed(0)
+        params = [torch.nn.Parameter(torch.randn(s, generator=gen) * 0.02) for s in SHAPES]
+        opt = ShardedFourBitAdamW(params, lr=1e-3, backend=CpuBackend(), reduce_grads=True)
+        for step in range(steps):
+            opt.zero_grad()
+            for p in params:
+                per_rank = [torch.randn(p.shape, generator=gen) * 1e-3 for _ in range(world)]
+                if step % 2:
+                    p.grad.add_(per_rank[rank])        # accumulate into the flat buffer, like backward does
+                else:
+                    p.grad = per_rank[rank].clone()    # a gradient produced elsewhere: copied in by the step
+            opt.step()
+        if rank == 0:
+            torch.save([p.detach().clone() for p in params], out)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gradients_reduced_inside_the_step_with_gloo_ranks(tmp_path):
+    world, steps = 2, 4
+    out = str(tmp_path / "params.pt")
+    mp.spawn(_worker_reduce, args=(world, _free_port(), steps, out), nprocs=world, join=True)
+    got = torch.load(out)
+    gen = torch.Generator().manual_seed(0)
+    params = [torch.randn(s, generator=gen) * 0.02 for s in SHAPES]
+    states = [TO.TensorState.zeros(s) for s in SHAPES]
+    for _ in range(steps):
+        for p, st in zip(params, states):
+            per_rank = [torch.randn(p.shape, generator=gen) * 1e-3 for _ in range(world)]
+            TO.step_tensor(p, (per_rank[0] + per_rank[1]) * 0.5, st, 1e-3, 0.9, 0.999, 1e-8, 0.01)
+    for i, (a, b) in enumerate(zip(got, params)):
+        assert torch.equal(a, b), f"tensor {i} {SHAPES[i]} differs in {(a != b).sum()} places"
