@@ -178,6 +178,27 @@ def test_late_steps_where_the_bias_correction_has_rounded_to_one():
         _assert_same(params, ostates, gparams, gstates, f"step {30001 + step}")
 
 
+@pytest.mark.parametrize("hp", [
+    dict(lr=1.0, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0),
+    dict(lr=3e-4, betas=(0.5, 0.9), eps=1e-6, weight_decay=0.1),
+    dict(lr=1e-2, betas=(0.99, 0.9999), eps=1e-10, weight_decay=1e-3),
+    dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-15, weight_decay=0.01),     # eps below the range of the packed sequences
+    dict(lr=1e-5, betas=(0.0001, 0.5), eps=1.0, weight_decay=10.0),
+])
+def test_other_hyper_parameters_bit_exact(hp):
+    gen, params, ostates, gparams, gstates = _make_problem(RAGGED, seed=3)
+    stepper = AbiStepper(gparams, gstates, **hp)
+    args = (hp["lr"], hp["betas"][0], hp["betas"][1], hp["eps"], hp["weight_decay"])
+    for step in range(5):
+        scale = [1e-3, 1.0, 1e-6, 30.0, 0.0][step]     # ordinary, large, tiny, huge and all-zero gradients
+        grads = [make_grad(p.shape, p.dtype, sigma=1e-3, gen=gen) * scale for p in params]
+        for p, g, st in zip(params, grads, ostates):
+            CO.step_tensor(p, g, st, *args)
+        stepper.step([g.to(DEV) for g in grads])
+        _assert_same(params, ostates, gparams, gstates, f"{hp} step {step + 1}")
+    assert stepper.status() == 0
+
+
 def test_multi_tensor_step_teacher_forced():
     """Each step starts from the oracle's state, so a mismatch cannot hide behind an earlier one."""
     gen, params, ostates, gparams, gstates = _make_problem(RAGGED, seed=1)
