@@ -137,6 +137,14 @@ def run(args, hp) -> None:
         push_ms = _max_over_ranks(push_ms, dev)
 
     shard_elements, flat_total = opt.layout.shard, opt.layout.total
+    # kernels of this library per step on this rank: clear / reciprocals / commit, plus one pre and one main kernel
+    # per mapping that has work (whole-row pieces with a column count that is a multiple of 256 take the panel mapping)
+    from .zero1 import RANK1
+    recs = [st.rec for st in opt.states]
+    panel = any(r.kind == RANK1 and not r.partial and r.cols % 256 == 0 for r in recs)
+    flat_r1 = any(r.kind == RANK1 and (r.partial or r.cols % 256) for r in recs)
+    flat_other = any(r.kind != RANK1 for r in recs)
+    launches_per_step = 3 + 2 * int(panel) + int(flat_r1) + int(flat_r1 or flat_other)
     # end to end: this rank's slices of the gradients arrive from pinned host memory every step
     e2e = None
     if reduce_grads:
@@ -206,7 +214,7 @@ def run(args, hp) -> None:
                              "GBps_per_gpu": gather_bytes / (push_ms * 1e-3) / 1e9, "link_peak_GBps": 770.0,
                              "target_ms": max(parts[1], gather_bytes / 770e9 * 1e3),
                              "note": "target = the slower of the plain main pass and the bytes that must leave the GPU over the measured peer-copy bandwidth"}},
-            "e2e": e2e, "gpu_launches": 6 * args.steps, "clocks": clocks, "also": also,
+            "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks, "also": also,
         }
         print(json.dumps(out))
     dist.destroy_process_group()
