@@ -555,9 +555,12 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
     };
     uint32_t e = static_cast<uint32_t>(r0) * cols + j0;
     RowScalars sc_next = fetch_scalars(r0, e);
+    uint32_t bad = 0;  // non-finite block scales seen in this item (reported once, at the end)
     int slot = 0;
     for (int r = r0; r < r1; ++r, e += cols) {
-        if (r_issue < r1) issue(e_issue, slot == 0 ? kStages - 1 : slot - 1);  // refill the slot the previous row used
+        // refill the slot the previous row used; past the end the last row is staged again (nobody reads it):
+        // cheaper than a branch around four copies
+        issue(r_issue < r1 ? e_issue : e, slot == 0 ? kStages - 1 : slot - 1);
         cp_async_commit();
         e_issue += cols;
         ++r_issue;
@@ -569,7 +572,7 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
         cp_async_wait<kStages - 1>();  // everything but the newest kStages-1 groups has landed: row r is there
         const char* base = stage + slot * kRowBytes;
         slot = slot + 1 == kStages ? 0 : slot + 1;
-        if (!(col_fast && sc.rrow == sc.rrow && sc.row_old > 0.0f)) {  // warp-uniform
+        if (!__all_sync(kFull, col_fast && sc.rrow == sc.rrow && sc.row_old > 0.0f)) {  // the vote tells the compiler it is uniform
             main_panel_row_exact<T>(tp, e, r, j0, hd, s, status, PUSH ? push : nullptr);
             continue;
         }
@@ -612,12 +615,11 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
         *reinterpret_cast<uint32_t*>(vc + (e >> 1)) = wq;
         const float ms_new = absmax_pairs_to_block(m);
         *reinterpret_cast<uint32_t*>(mc + (e >> 1)) = quantize_m8(m, ms_new, s);
-        if ((lane & 15) == 0) {
-            t.ms[e >> 7] = ms_new;
-            if (nonfinite(ms_new)) atomicOr(status, QF_STATUS_NONFINITE);
-        }
+        if ((lane & 15) == 0) t.ms[e >> 7] = ms_new;
+        bad = max(bad, __float_as_uint(ms_new));  // ms_new >= 0 or NaN: the largest bit pattern seen, checked after the loop
     }
     cp_async_wait<0>();
+    if (bad >= 0x7f800000u && (lane & 15) == 0) atomicOr(status, QF_STATUS_NONFINITE);
 }
 
 // =================================================================================================
