@@ -287,13 +287,18 @@ __device__ __forceinline__ uint32_t quantize_m8(const f2 (&m)[4], float scale, c
     return w;
 }
 
-// Max of |x| over the 128-element block a lane's 8 values belong to: 16 lanes, one redux instruction on
-// the bit patterns (non-negative floats order like unsigned integers); each half-warp names its own lanes.
+// Max of |x| over the 128-element block a lane's 8 values belong to (16 lanes), by redux instructions on the
+// bit patterns (non-negative floats order like unsigned integers).
 __device__ __forceinline__ float absmax_pairs_to_block(const f2 (&m)[4]) {
     float a = fmaxf(fmaxf(fabsf(m[0].x), fabsf(m[0].y)), fmaxf(fabsf(m[1].x), fabsf(m[1].y)));
     a = fmaxf(a, fmaxf(fmaxf(fabsf(m[2].x), fabsf(m[2].y)), fmaxf(fabsf(m[3].x), fabsf(m[3].y))));
-    const unsigned mask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
-    return __uint_as_float(__reduce_max_sync(mask, __float_as_uint(a)));
+    // two full-warp reductions, each over one half's values (the other half contributes 0): a reduction under
+    // a half-warp mask is compiled into a guarded collective with its own branches and warp syncs
+    const bool hi = threadIdx.x & 16;
+    const uint32_t bits = __float_as_uint(a);
+    const uint32_t lo_max = __reduce_max_sync(kFull, hi ? 0u : bits);
+    const uint32_t hi_max = __reduce_max_sync(kFull, hi ? bits : 0u);
+    return __uint_as_float(hi ? hi_max : lo_max);
 }
 
 // ---- cp.async helpers (per-lane asynchronous copies global -> shared) -------------------------------------
