@@ -27,9 +27,11 @@ int fail(int code, const char* fmt, ...) {
 #define QF_CUDA(call)                                                                          \
     do {                                                                                       \
         cudaError_t e_ = (call);                                                               \
-        if (e_ != cudaSuccess)                                                                 \
+        if (e_ != cudaSuccess) {                                                               \
+            (void)cudaGetLastError(); /* a refused call must not leave its code for the host's next check */ \
             return fail(e_ == cudaErrorNoDevice || e_ == cudaErrorInsufficientDriver ? QF_ERR_NO_DEVICE : QF_ERR_CUDA, \
                         "%s failed: %s", #call, cudaGetErrorString(e_));                      \
+        }                                                                                      \
     } while (0)
 
 constexpr size_t kStatusBytes = 256;  // head of the workspace: status word, then padding

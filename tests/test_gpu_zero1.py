@@ -169,3 +169,25 @@ def test_state_moves_between_sharded_and_unsharded_optimizers(dtype):
         emulated_step(ranks2, gs)
     for i, (p, w) in enumerate(zip(ranks2[1][0], want)):
         assert torch.equal(p.detach().cpu(), w), f"tensor {i} {SHAPES[i]} differs in {(p.detach().cpu() != w).sum()} places"
+
+
+def test_peer_functions_report_errors_instead_of_faulting():
+    import ctypes as C
+    from quantfour_adamw_cuda_b200 import _lib
+    L = _lib.lib()
+    base = C.c_void_p(0)
+    # a handle of zeros names no allocation: the call must fail with a message, not crash
+    rc = L.qf_peer_open(bytes(64), 0, C.byref(base))
+    assert rc != 0 and L.qf_last_error()
+    # closing something that was never opened
+    x = torch.zeros(16, device="cuda")
+    with pytest.raises(ValueError, match="not a mapping"):
+        _lib.check(L.qf_peer_close(C.c_void_p(x.data_ptr()), 0), "qf_peer_close")
+    # exporting a host pointer
+    buf = (C.c_char * 64)()
+    off = C.c_int64(0)
+    host = torch.zeros(16)
+    rc = L.qf_peer_export(C.c_void_p(host.data_ptr()), 0, buf, C.byref(off))
+    assert rc != 0 and L.qf_last_error()
+    torch.cuda.synchronize()
+    assert float(x.sum()) == 0.0          # the context is still usable
