@@ -505,8 +505,9 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
     // Element offsets inside the tensor fit 32 bits (the host gives larger tensors the flat mapping), so a
     // row costs one 32-bit add per running offset and one widening add per address.
     const uint32_t cols = static_cast<uint32_t>(t.cols);
-    auto issue = [&](uint32_t e, int slot) {
-        char* base = stage + slot * kRowBytes;
+    static_assert(kStages == 2, "the loop below stages exactly one row ahead and flips between two slots");
+    auto issue = [&](uint32_t e, uint32_t slot_off) {
+        char* base = stage + slot_off;
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
             cp_async16(base + (v * 32 + lane) * 16, t.p + static_cast<size_t>(e) * sizeof(T) + v * 16);
@@ -515,15 +516,8 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
         cp_async4(base + 2 * kArr + lane * 4, mc + (e >> 1));
         cp_async4(base + 2 * kArr + 128 + lane * 4, vc + (e >> 1));
     };
-    uint32_t e_issue = static_cast<uint32_t>(r0) * cols + j0;  // next row to stage
-    int r_issue = r0;
-#pragma unroll
-    for (int i = 0; i < kStages - 1; ++i) {
-        if (r_issue < r1) issue(e_issue, i);
-        cp_async_commit();  // one group per row, empty past the end, so that the group count stays in step
-        e_issue += cols;
-        ++r_issue;
-    }
+    issue(static_cast<uint32_t>(r0) * cols + j0, 0);  // the first row of the item
+    cp_async_commit();
 
     // The pass that stored the reciprocals wrote NaN where an old or new maximum is outside the range of
     // the fast sequences.  A zero old maximum (first step, rows never touched) lets v fall below the range
@@ -561,22 +555,19 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
     uint32_t e = static_cast<uint32_t>(r0) * cols + j0;
     RowScalars sc_next = fetch_scalars(r0, e);
     uint32_t bad = 0;  // non-finite block scales seen in this item (reported once, at the end)
-    int slot = 0;
+    uint32_t off = 0;  // byte offset of the ring slot that holds row r; the other slot is off ^ kRowBytes
     for (int r = r0; r < r1; ++r, e += cols) {
-        // refill the slot the previous row used; past the end the last row is staged again (nobody reads it):
-        // cheaper than a branch around four copies
-        issue(r_issue < r1 ? e_issue : e, slot == 0 ? kStages - 1 : slot - 1);
+        // Stage the next row into the slot the previous row used and fetch its scalars.  Past the end the last
+        // row is staged and fetched again (nobody reads it): cheaper than a branch around the copies.
+        const bool more = r + 1 < r1;
+        const uint32_t e_next = more ? e + cols : e;
+        issue(e_next, off ^ kRowBytes);
         cp_async_commit();
-        e_issue += cols;
-        ++r_issue;
         const RowScalars sc = sc_next;
-        {
-            const int rn = min(r + 1, r1 - 1);  // past the end: fetch the last row again instead of branching
-            sc_next = fetch_scalars(rn, rn == r ? e : e + cols);
-        }
-        cp_async_wait<kStages - 1>();  // everything but the newest kStages-1 groups has landed: row r is there
-        const char* base = stage + slot * kRowBytes;
-        slot = slot + 1 == kStages ? 0 : slot + 1;
+        sc_next = fetch_scalars(more ? r + 1 : r, e_next);
+        cp_async_wait<1>();  // everything but the newest group has landed: row r is there
+        const char* base = stage + off;
+        off ^= kRowBytes;
         if (!__all_sync(kFull, col_fast && sc.rrow == sc.rrow && sc.row_old > 0.0f)) {  // the vote tells the compiler it is uniform
             main_panel_row_exact<T>(tp, e, r, j0, hd, s, status, PUSH ? push : nullptr);
             continue;
