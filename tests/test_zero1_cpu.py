@@ -274,3 +274,39 @@ def test_gradients_reduced_inside_the_step_with_gloo_ranks(tmp_path):
             TO.step_tensor(p, (per_rank[0] + per_rank[1]) * 0.5, st, 1e-3, 0.9, 0.999, 1e-8, 0.01)
     for i, (a, b) in enumerate(zip(got, params)):
         assert torch.equal(a, b), f"tensor {i} {SHAPES[i]} differs in {(a != b).sum()} places"
+
+
+def test_flat_gradient_buffer_without_a_process_group():
+    """reduce_grads=True in a single process: gradients become views of one flat buffer, zero_grad keeps them
+    attached, a gradient assigned from outside is copied in, and the step matches the oracle."""
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from sharded_cpu_backend import CpuBackend
+    from quantfour_adamw_cuda_b200.zero1 import ShardedFourBitAdamW
+    gen = torch.Generator().manual_seed(4)
+    params = [torch.nn.Parameter(torch.randn(s, generator=gen) * 0.02) for s in SHAPES]
+    ref = [p.detach().clone() for p in params]
+    states = [TO.TensorState.zeros(s) for s in SHAPES]
+    opt = ShardedFourBitAdamW(params, lr=1e-3, backend=CpuBackend(), reduce_grads=True)
+    base = opt.flat_grad.data_ptr()
+    assert all(p.grad is not None and base <= p.grad.data_ptr() < base + opt.flat_grad.numel() * 4 for p in params)
+    for step in range(3):
+        opt.zero_grad()
+        assert float(opt.flat_grad.abs().sum()) == 0.0
+        grads = [torch.randn(p.shape, generator=gen) * 1e-3 for p in params]
+        for i, (p, g) in enumerate(zip(params, grads)):
+            if i % 2:
+                p.grad = g.clone()         # replaced from outside
+            else:
+                p.grad.add_(g)             # accumulated in place
+        for r, g, st in zip(ref, grads, states):
+            TO.step_tensor(r, g, st, 1e-3, 0.9, 0.999, 1e-8, 0.01)
+        opt.step()
+        assert all(base <= p.grad.data_ptr() < base + opt.flat_grad.numel() * 4 for p in params)
+    assert all(torch.equal(p.detach(), r) for p, r in zip(params, ref))
+
+
+def test_constructor_rejects_unknown_comm():
+    from quantfour_adamw_cuda_b200.zero1 import ShardedFourBitAdamW
+    with pytest.raises(ValueError, match="comm must be"):
+        ShardedFourBitAdamW([torch.nn.Parameter(torch.zeros(8))], comm="smoke-signals", backend=object())
