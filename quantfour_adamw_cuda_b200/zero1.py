@@ -257,6 +257,16 @@ class CudaBackend:
         arr = (C.c_int64 * len(deltas))(*deltas)
         self._call(self.L.qf_step_main_push, states, hyper, arr, len(deltas))
 
+    def read_status(self) -> int:
+        """Synchronise the current stream, return the status word of this backend's workspace and clear it."""
+        if self.ws is None:
+            return 0
+        word = C.c_uint32(0)
+        dev = self.ws.device
+        _lib.check(self.L.qf_read_status(self.ws.data_ptr(), dev.index,
+                                         C.c_void_p(torch.cuda.current_stream(dev).cuda_stream), C.byref(word)), "qf_read_status")
+        return word.value
+
     # ---- the flat buffer in the other processes of the node -----------------------------------------
 
     def export_buffer(self, t: torch.Tensor) -> Tuple[bytes, int]:
@@ -508,6 +518,12 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
         if multi:
             self._all_gather()
         return loss
+
+    def nonfinite_seen(self) -> bool:
+        """Synchronise and report whether any step of this rank since the last call produced a non-finite scale
+        (a non-finite gradient, or an overflow): the same question FourBitAdamW.nonfinite_seen answers."""
+        read = getattr(self.backend, "read_status", None)
+        return bool(read() & _lib.QF_STATUS_NONFINITE) if read else False
 
     @torch.no_grad()
     def step_pre(self) -> None:

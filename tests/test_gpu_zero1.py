@@ -191,3 +191,16 @@ def test_peer_functions_report_errors_instead_of_faulting():
     assert rc != 0 and L.qf_last_error()
     torch.cuda.synchronize()
     assert float(x.sum()) == 0.0          # the context is still usable
+
+
+def test_sharded_optimizer_reports_nonfinite_gradients():
+    params = [torch.nn.Parameter(torch.randn(128, 256, device="cuda") * 0.02), torch.nn.Parameter(torch.randn(5000, device="cuda"))]
+    opt = ShardedFourBitAdamW(params, lr=1e-3)
+    for p in params:
+        p.grad = torch.randn_like(p) * 1e-3
+    opt.step()
+    assert not opt.nonfinite_seen()
+    params[0].grad[3, 5] = float("inf")
+    opt.step()
+    assert opt.nonfinite_seen()
+    assert not opt.nonfinite_seen()      # reading clears the word
