@@ -226,7 +226,7 @@ def single_gpu(args):
     ev[0].record()
     for i in range(args.steps):
         set_grads(i)
-        opt.step()
+        opt.step(grad_scale=args.grad_scale)
         ev[i + 1].record()
     torch.cuda.synchronize(dev)
     total_ms = ev[0].elapsed_time(ev[-1])
@@ -246,7 +246,7 @@ def single_gpu(args):
         for st in opt.state.values():
             st["step"] += 1
         h = (_lib.QfHyper * 1)(qf.make_hyper(HP["lr"], *HP["betas"], HP["eps"], HP["weight_decay"],
-                                             float(next(iter(opt.state.values()))["step"])))
+                                             float(next(iter(opt.state.values()))["step"]), args.grad_scale or 1.0))
         a = (plan.descs, len(plan.descs), h, 1, plan.workspace.data_ptr(), plan.workspace.numel(), dev.index, stream)
         e[0].record()
         _lib.check(L.qf_step_pre(*a), "qf_step_pre")
@@ -290,7 +290,7 @@ def single_gpu(args):
         "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload, "tensors": len(shapes), "params": n_params, "param_dtype": "bf16",
-                   "start_step": args.start_step,
+                   "start_step": args.start_step, "grad_scale": args.grad_scale,
                    "state": "4-bit m (block-128) + 4-bit v (rank-1 / block-128), fp32 for numel <= 4096",
                    "l2": "inputs (%.1f GB per step) are far larger than L2" % (alg_bytes / 1e9),
                    "ms_per_step_min": min(per_step), "ms_per_step_max": max(per_step)},
@@ -366,6 +366,9 @@ def main():
                          "regime where sqrt(1 - beta2^t) has rounded to 1)")
     ap.add_argument("--reduce-grads", action="store_true",
                     help="N>1: the step starts with a reduce-scatter (mean) of per-rank gradients kept in a flat buffer")
+    ap.add_argument("--grad-scale", type=float, default=None,
+                    help="N=1: pass this factor to every timed step (the first pass then rewrites the gradients scaled); "
+                         "use a value next to 1, e.g. 1.0000001, so that repeated steps do not drive the data to zero")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

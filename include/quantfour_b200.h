@@ -69,7 +69,10 @@ typedef struct QfHyper {
     float eps;       /* eps                            */
     float neg_step;  /* -(lr / (1 - beta1^step))       */
     float bc2s;      /* sqrt(1 - beta2^step)           */
-    float pad;
+    float grad_scale; /* 0 or 1: gradients are used as they are.  Otherwise every gradient of the tensors that use
+                         this set is replaced in place by RN(g * grad_scale), in g's own dtype, before the step uses
+                         it (loss-scale removal or a clipping factor without a pass of its own).  No counterpart
+                         in the reference.  With the split entry points, pass the same value to both halves.  */
 } QfHyper;
 
 /* One tensor of a multi-tensor step.  Replaces the per-tensor argument list of the reference's

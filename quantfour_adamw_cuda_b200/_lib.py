@@ -23,7 +23,7 @@ QF_NOALLOC_MAX_ROWS_PLUS_COLS = 131072
 
 
 class QfHyper(C.Structure):
-    _fields_ = [(n, C.c_float) for n in ("decay", "w1", "beta2", "w2", "eps", "neg_step", "bc2s", "pad")]
+    _fields_ = [(n, C.c_float) for n in ("decay", "w1", "beta2", "w2", "eps", "neg_step", "bc2s", "grad_scale")]
 
 
 class QfTensorDesc(C.Structure):

@@ -225,14 +225,22 @@ void roll(const Plan& pl, int mode, cudaStream_t stream) {
     qf::rank1_roll_kernel<<<pl.n * qf::kRollSlices, qf::kThreads, 0, stream>>>(pl.d_tensors, pl.n, mode);
 }
 
-int launch_pre(const Plan& pl, const qf::HyperPack& hp, cudaStream_t stream) {
+template <bool SCALE>
+int launch_pre_panel(const Plan& pl, const qf::HyperPack& hp, cudaStream_t stream) {
+    const int dyn = qf::pre_dyn_smem(pl.any_f32_panel);
+    QF_CUDA(cudaFuncSetAttribute(qf::step_pre_kernel<true, SCALE>, cudaFuncAttributeMaxDynamicSharedMemorySize, qf::pre_dyn_smem(true)));
+    qf::step_pre_kernel<true, SCALE><<<persistent_grid(pl.items[kPrePanel], QF_PRE_MIN_CTAS), qf::kThreads, dyn, stream>>>(
+        pl.d_tensors, pl.d_base[kPrePanel], pl.n, hp, dyn / qf::kWarpsPerCta, pl.d_status);
+    return QF_OK;
+}
+
+int launch_pre(const Plan& pl, const qf::HyperPack& hp, int n_hypers, cudaStream_t stream) {
     if (pl.n_rank1 == 0) return QF_OK;
     roll(pl, qf::kRollClear, stream);
     if (pl.items[kPrePanel]) {
-        const int dyn = qf::pre_dyn_smem(pl.any_f32_panel);
-        QF_CUDA(cudaFuncSetAttribute(qf::step_pre_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, qf::pre_dyn_smem(true)));
-        qf::step_pre_kernel<true><<<persistent_grid(pl.items[kPrePanel], QF_PRE_MIN_CTAS), qf::kThreads, dyn, stream>>>(
-            pl.d_tensors, pl.d_base[kPrePanel], pl.n, hp, dyn / qf::kWarpsPerCta, pl.d_status);
+        bool scaled = false;  // the variant that rewrites the gradients runs only when some set asks for it
+        for (int k = 0; k < n_hypers; ++k) scaled = scaled || hp.h[k].gs != 1.0f;
+        if (int rc = scaled ? launch_pre_panel<true>(pl, hp, stream) : launch_pre_panel<false>(pl, hp, stream)) return rc;
     }
     if (pl.items[kPreFlat])
         qf::step_pre_kernel<false><<<persistent_grid(pl.items[kPreFlat], QF_PRE_MIN_CTAS), qf::kThreads, 0, stream>>>(
@@ -292,7 +300,7 @@ qf::HyperDev widen_hyper(const QfHyper& h) {
     d.h = h;
     d.rb = static_cast<float>(1.0 / static_cast<double>(h.bc2s));  // double rounding is harmless for 1/x
     d.nb = -h.bc2s;
-    d.pad = 0;
+    d.gs = h.grad_scale == 0.0f ? 1.0f : h.grad_scale;
     const float all[] = {h.decay, h.w1, h.beta2, h.w2, h.eps, h.neg_step, h.bc2s};
     bool ok = true;
     for (float x : all) ok = ok && std::isfinite(x);
@@ -314,7 +322,7 @@ int step_common(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers,
     memset(&hp, 0, sizeof hp);
     for (int k = 0; k < n_hypers; ++k) hp.h[k] = widen_hyper(hypers[k]);
     if (pre)
-        if (int rc = launch_pre(pl, hp, st)) return rc;
+        if (int rc = launch_pre(pl, hp, n_hypers, st)) return rc;
     if (main_)
         if (int rc = launch_main(pl, hp, n_hypers, st, push)) return rc;
     return QF_OK;
@@ -353,7 +361,7 @@ void qf_make_hyper(double lr, double beta1, double beta2, double eps, double wei
     out->eps = static_cast<float>(eps);
     out->neg_step = static_cast<float>(-(lr / bc1));
     out->bc2s = static_cast<float>(std::sqrt(bc2));
-    out->pad = 0.0f;
+    out->grad_scale = 0.0f;
 }
 
 int qf_step_multi(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,
@@ -729,7 +737,7 @@ int qf_step_rank1_noalloc(void* p, const void* g, void* m_codes, void* v_codes, 
     qf::HyperPack hp;
     memset(&hp, 0, sizeof hp);
     hp.h[0] = widen_hyper(*hyper);
-    if (int rc = launch_pre(pl, hp, st)) return rc;   // clears the new maxima first: the array keeps the last call's
+    if (int rc = launch_pre(pl, hp, 1, st)) return rc;   // clears the new maxima first: the array keeps the last call's
     return launch_main(pl, hp, 1, st);
 }
 

@@ -67,8 +67,16 @@ struct HyperDev {
     float rb;    // RN(1 / bc2s)
     float nb;    // -bc2s
     int32_t fast;  // 0: the scalars are outside the ranges the fast sequences cover -> exact path only
-    int32_t pad;
+    float gs;      // gradient scale (1 = none): g is replaced in place by RN(g * gs) in its own dtype before it is used
 };
+
+// x as a value of the parameter / gradient dtype (what a store followed by a load would give).
+template <typename T>
+__device__ __forceinline__ float round_as(float x);
+template <>
+__device__ __forceinline__ float round_as<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ float round_as<__nv_bfloat16>(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 struct HyperPack {
     HyperDev h[QF_MAX_HYPERS];
 };
@@ -336,7 +344,7 @@ __device__ __forceinline__ void cp_async_wait() {
 constexpr int kPreStages = 8;
 constexpr int pre_dyn_smem(bool any_f32) { return kWarpsPerCta * kPreStages * 32 * ((any_f32 ? 32 : 16) + 4); }
 
-template <typename T>
+template <typename T, bool SCALE>
 __device__ __forceinline__ void pre_panel(const DevTensor& t, int64_t li, const HyperDev& hd, const SmemPre& s,
                                           char* stage, uint32_t* status) {
     static_assert(kPreRowsPerItem == 64, "two old row maxima per lane");
@@ -389,6 +397,11 @@ __device__ __forceinline__ void pre_panel(const DevTensor& t, int64_t li, const 
         const float row_old = __shfl_sync(kFull, k_row < 32 ? rows_lo : rows_hi, k_row & 31);
         float g[8];
         g_raw.widen(g);
+        if (SCALE) {  // the scaled gradient replaces the original: the main pass and the caller see it
+#pragma unroll
+            for (int k = 0; k < 8; ++k) g[k] = round_as<T>(__fmul_rn(g[k], hd.gs));
+            Elem<T>::store8(const_cast<char*>(t.g), static_cast<int64_t>(static_cast<uint32_t>(r) * cols + j0), g);
+        }
         uint32_t rmax = 0;
         if (hd.fast) {  // warp-uniform
 #pragma unroll
@@ -690,6 +703,11 @@ __device__ __forceinline__ void pre_flat_rank1(const DevTensor& t, int64_t li, c
         float g[8], sc[8];
         int ri[8], ci[8];
         load8_masked<T>(t.g, e, nv, vec, g);
+        if (hd.gs != 1.0f) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) g[k] = round_as<T>(__fmul_rn(g[k], hd.gs));
+            store8_masked<T>(const_cast<char*>(t.g), e, nv, vec, g);
+        }
         const uint32_t wv = load_codes(vc, e, nv, vec);
         rank1_scales(t.vs, t.vcol, e + t.flat_off, nv, t.cols, sc, ri, ci);
 #pragma unroll
@@ -857,6 +875,15 @@ __device__ __forceinline__ void main_flat(const DevTensor* tp, int64_t li, const
     for (int it = 0; it < kRowsPerItem; ++it) {
         const int64_t wbase = start + static_cast<int64_t>(it) * kPanelCols;
         if (wbase >= t.numel) break;  // warp-uniform
+        if (KIND != QF_KIND_RANK1 && hd.gs != 1.0f) {  // no first pass for these kinds: the gradient is scaled here
+            const int64_t e = wbase + (threadIdx.x & 31) * 8;
+            const int nv = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(8), t.numel - e)));
+            float g[8];
+            load8_masked<T>(t.g, e, nv, vec, g);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) g[k] = round_as<T>(__fmul_rn(g[k], hd.gs));
+            store8_masked<T>(const_cast<char*>(t.g), e, nv, vec, g);
+        }
         if (KIND != QF_KIND_RANK1 && hd.fast && vec && wbase + kPanelCols <= t.numel)
             main_flat_run_fast<T, KIND>(t, wbase, h2, s, status, push);
         else
@@ -874,7 +901,8 @@ __device__ __forceinline__ void main_flat(const DevTensor* tp, int64_t li, const
 #ifndef QF_PRE_MIN_CTAS
 #define QF_PRE_MIN_CTAS 3
 #endif
-template <bool PANEL>
+// SCALE (panel mapping): some hyper-parameter set of the launch carries a gradient scale other than 1.
+template <bool PANEL, bool SCALE = false>
 __global__ void __launch_bounds__(kThreads, QF_PRE_MIN_CTAS)
 step_pre_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict__ base, int n,
                 const __grid_constant__ HyperPack hp, int ring_bytes, uint32_t* status) {
@@ -890,9 +918,9 @@ step_pre_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict
         const HyperDev& h = hp.h[t.hyper];
         if (PANEL) {
             if (t.dtype == QF_BF16)
-                pre_panel<__nv_bfloat16>(t, li, h, s, stage, status);
+                pre_panel<__nv_bfloat16, SCALE>(t, li, h, s, stage, status);
             else
-                pre_panel<float>(t, li, h, s, stage, status);
+                pre_panel<float, SCALE>(t, li, h, s, stage, status);
         } else {
             if (t.dtype == QF_BF16)
                 pre_flat_rank1<__nv_bfloat16>(t, li, h, s, status);

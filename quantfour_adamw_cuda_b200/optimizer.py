@@ -44,12 +44,15 @@ def enable_param_quantization(p, threshold) -> bool:
     return True
 
 
-def make_hyper(lr: float, beta1: float, beta2: float, eps: float, weight_decay: float, step: float) -> _lib.QfHyper:
+def make_hyper(lr: float, beta1: float, beta2: float, eps: float, weight_decay: float, step: float,
+               grad_scale: float = 1.0) -> _lib.QfHyper:
     """Scalars of one step, derived in Python doubles like the reference's PyTorch path
-    (adamw_fourbit_triton.py:415, :458-465) and rounded once to float32 by ctypes."""
+    (adamw_fourbit_triton.py:415, :458-465) and rounded once to float32 by ctypes.  `grad_scale` other than 1
+    makes the step replace every gradient by g * grad_scale (rounded to g's dtype) before using it."""
     bc1 = 1 - beta1 ** step
     bc2 = 1 - beta2 ** step
-    return _lib.QfHyper(1 - lr * weight_decay, 1 - beta1, beta2, 1 - beta2, eps, -(lr / bc1), math.sqrt(bc2), 0.0)
+    return _lib.QfHyper(1 - lr * weight_decay, 1 - beta1, beta2, 1 - beta2, eps, -(lr / bc1), math.sqrt(bc2),
+                        0.0 if grad_scale == 1.0 else grad_scale)
 
 
 def state_kind(p: torch.Tensor, threshold: int) -> int:
@@ -235,12 +238,18 @@ class FourBitAdamW(torch.optim.Optimizer):
             d.v_scale = vo["max1"].data_ptr()
 
     @torch.no_grad()
-    def step(self, closure=None):
-        """Perform a single optimization step (fused_quantfour.py:131-138); returns the closure's loss."""
+    def step(self, closure=None, *, grad_scale: Optional[float] = None):
+        """Perform a single optimization step (fused_quantfour.py:131-138); returns the closure's loss.
+
+        `grad_scale` (not in the reference): a factor every gradient is multiplied by, in place and rounded to
+        its own dtype, before the step uses it -- the inverse loss scale, a clipping coefficient.  For 2-D tensors
+        the multiplication rides the pass that reads the gradients anyway, so it costs no pass of its own.  A
+        gradient that had to be made contiguous is scaled in the copy only."""
         loss = None
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
+        self._grad_scale = 1.0 if grad_scale is None else float(grad_scale)
 
         if self._fast is not None and self._step_fast():
             return loss
@@ -278,7 +287,7 @@ class FourBitAdamW(torch.optim.Optimizer):
                 hi = hyper_index.get(key)
                 if hi is None:
                     hi = hyper_index[key] = len(hypers)
-                    hypers.append(make_hyper(*gkey, t))
+                    hypers.append(make_hyper(*gkey, t, self._grad_scale))
                 work.setdefault(p.device, []).append((p, g, st, hi))
 
         for dev, entries in work.items():
@@ -348,7 +357,7 @@ class FourBitAdamW(torch.optim.Optimizer):
             c[1] += 1.0
             group = self.param_groups[c[0]]
             beta1, beta2 = group["betas"]
-            hypers.append(make_hyper(group["lr"], beta1, beta2, group["eps"], group["weight_decay"], c[1]))
+            hypers.append(make_hyper(group["lr"], beta1, beta2, group["eps"], group["weight_decay"], c[1], self._grad_scale))
         dev = f["dev"]
         harr = (_lib.QfHyper * len(hypers))(*hypers)
         rc = _lib.lib().qf_step_multi(plan.descs, len(plan.descs), harr, len(hypers), plan.workspace.data_ptr(),

@@ -493,7 +493,9 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
     # ---- step -------------------------------------------------------------------------------------
 
     @torch.no_grad()
-    def step(self, closure=None):
+    def step(self, closure=None, *, grad_scale: Optional[float] = None):
+        """One step.  `grad_scale`: see FourBitAdamW.step (every rank passes the same value)."""
+        self._grad_scale = 1.0 if grad_scale is None else float(grad_scale)
         loss = None
         if closure is not None:
             with torch.enable_grad():
@@ -544,7 +546,8 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
             st.g = flat_grads[st.rec.tensor][st.rec.a:st.rec.b]
         self.step_count += 1
         beta1, beta2 = group["betas"]
-        self._hyper = make_hyper(group["lr"], beta1, beta2, group["eps"], group["weight_decay"], float(self.step_count))
+        self._hyper = make_hyper(group["lr"], beta1, beta2, group["eps"], group["weight_decay"], float(self.step_count),
+                                 getattr(self, "_grad_scale", 1.0))
         if self.shared_new.numel():
             self.shared_new.zero_()
         self.backend.pre(self.states, self._hyper)

@@ -201,3 +201,36 @@ def test_tensor_with_more_than_2_to_31_elements():
     joined = torch.cat([o2.state[h]["momentum_qstate"]["overhead"]["max1"] for h in halves])
     assert torch.equal(s1["momentum_qstate"]["overhead"]["max1"], joined)
     assert not o1.nonfinite_seen()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("scale", [1.0 / 1024, 0.37])
+def test_grad_scale_equals_scaling_the_gradients_first(dtype, scale):
+    """step(grad_scale=s) leaves the same parameters and state as multiplying every gradient by s (rounded to its
+    dtype) and stepping, and the gradients themselves end up scaled in place -- for every mapping: panel and flat
+    rank-1, block-128, fp32 state."""
+    import numpy as np
+    shapes = [(64, 256), (300, 77), (5000,), (1000,), (3, 5, 7, 99), (129, 255), (4096,), (256, 512)]
+    gen = torch.Generator().manual_seed(21)
+    init = [(torch.randn(s, generator=gen) * 0.02).to(dtype) for s in shapes]
+    pa = [nn.Parameter(p.clone().cuda()) for p in init]
+    pb = [nn.Parameter(p.clone().cuda()) for p in init]
+    oa, ob = qf.FourBitAdamW(pa, lr=1e-3), qf.FourBitAdamW(pb, lr=1e-3)
+    s32 = float(np.float32(scale))
+    for step in range(4):
+        grads = [(torch.randn(s, generator=gen) * 0.5).to(dtype) for s in shapes]
+        scaled = [(g.float() * s32).to(dtype) for g in grads]
+        for p, g in zip(pa, grads):
+            p.grad = g.clone().cuda()
+        for p, g in zip(pb, scaled):
+            p.grad = g.clone().cuda()
+        oa.step(grad_scale=scale)
+        ob.step()
+        for i, (a, b, g) in enumerate(zip(pa, pb, scaled)):
+            assert torch.equal(a.detach(), b.detach()), f"step {step} tensor {i} {shapes[i]}: parameters"
+            assert torch.equal(a.grad.cpu(), g), f"step {step} tensor {i} {shapes[i]}: gradient not scaled in place"
+    for a, b in zip(pa, pb):
+        sa, sb = oa.state[a], ob.state[b]
+        assert torch.equal(sa["exp_avg"], sb["exp_avg"]) and torch.equal(sa["exp_avg_sq"], sb["exp_avg_sq"])
+    oa.step()       # and a step without the argument goes back to unscaled gradients
+    assert not oa.nonfinite_seen()
