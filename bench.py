@@ -27,6 +27,7 @@ import subprocess
 import sys
 import time
 
+import numpy as np
 import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -293,7 +294,9 @@ def single_gpu(args):
                    "start_step": args.start_step, "grad_scale": args.grad_scale,
                    "state": "4-bit m (block-128) + 4-bit v (rank-1 / block-128), fp32 for numel <= 4096",
                    "l2": "inputs (%.1f GB per step) are far larger than L2" % (alg_bytes / 1e9),
-                   "ms_per_step_min": min(per_step), "ms_per_step_max": max(per_step)},
+                   "ms_per_step_min": min(per_step), "ms_per_step_max": max(per_step),
+                   "ms_per_step_median": float(np.median(per_step)), "ms_per_step_p10": float(np.percentile(per_step, 10)),
+                   "ms_per_step_p90": float(np.percentile(per_step, 90))},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": alg_bytes * TRAFFIC_PER_ALGORITHMIC_BYTE, "traffic_note": "scaled from the ncu capture on the "
                      "355 M-parameter set (profiles/step_main_pre_kernels_gpt2m.md)",
