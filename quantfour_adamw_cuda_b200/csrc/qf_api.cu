@@ -555,8 +555,11 @@ int qf_quantize_block(const float* x, int64_t numel, int map, uint8_t* codes, fl
     if (!scales) return fail(QF_ERR_BAD_ARG, "scales is null");
     QF_CUDA(cudaSetDevice(device));
     const int vec = aligned(x, 16) && aligned(codes, 4);
-    qf::quantize_block_kernel<<<persistent_grid(flat_items(numel), 8, 2), qf::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(x, numel, map, codes,
-                                                                                                      scales, vec);
+    const unsigned grid = persistent_grid(flat_items(numel), 8, 2);
+    if (map)
+        qf::quantize_block_kernel<1><<<grid, qf::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(x, numel, codes, scales, vec);
+    else
+        qf::quantize_block_kernel<0><<<grid, qf::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(x, numel, codes, scales, vec);
     QF_CUDA(cudaGetLastError());
     return QF_OK;
 }

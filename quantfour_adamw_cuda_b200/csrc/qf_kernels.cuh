@@ -1027,53 +1027,60 @@ rank1_roll_kernel(const DevTensor* __restrict__ tensors, int n, int mode) {
 // Stand-alone quantize / dequantize kernels (fp32 in / out)
 // =================================================================================================
 
-// Block-128 quantize: one warp item = kRowsPerItem runs of 256 elements.
+// Block-128 quantize: one warp item = kRowsPerItem runs of 256 elements.  MAP: 0 first-moment map (table search),
+// 1 second-moment map (closed form).  Items that lie wholly inside a vector-aligned tensor take a loop without
+// masks; the last item and unaligned tensors take the general one.
+template <int MAP>
 __global__ void __launch_bounds__(kThreads)
-quantize_block_kernel(const float* __restrict__ x, int64_t numel, int map, uint8_t* __restrict__ codes,
-                      float* __restrict__ scales, int vec) {
+quantize_block_kernel(const float* __restrict__ x, int64_t numel, uint8_t* __restrict__ codes, float* __restrict__ scales,
+                      int vec) {
     __shared__ Smem s;
     load_smem(s);
-    const float* mid = map ? s.t.mv : s.t.mm;
+    const float* mid = MAP ? s.t.mv : s.t.mm;
     const int lane = threadIdx.x & 31;
     // warps stride over the items, so that a CTA fills its search table once for many items
     const int64_t per_item = static_cast<int64_t>(kPanelCols) * kRowsPerItem;
     const int64_t total = (numel + per_item - 1) / per_item, stride = static_cast<int64_t>(gridDim.x) * kWarpsPerCta;
     for (int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5); item < total; item += stride) {
-    const int64_t start = item * per_item;
-    // the next run's input is requested before this run is worked on
-    auto fetch = [&](int64_t wbase, float (&dst)[8]) {
-        const int64_t e = wbase + lane * 8;
-        const int nv = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(8), numel - e)));
-        load8_masked<float>(reinterpret_cast<const char*>(x), e, nv, vec, dst);
-    };
-    float vn[8];
-    if (start < numel) fetch(start, vn);
-    for (int it = 0; it < kRowsPerItem; ++it) {
-        const int64_t wbase = start + static_cast<int64_t>(it) * kPanelCols;
-        if (wbase >= numel) break;
-        const int64_t e = wbase + lane * 8;
-        const int nv = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(8), numel - e)));
-        float v[8];
+        const int64_t start = item * per_item;
+        if (vec && start + per_item <= numel) {  // warp-uniform
+            const float4* src = reinterpret_cast<const float4*>(x + start) + lane * 2;
+            float4 na = src[0], nb = src[1];  // the next run's input is requested before this run is worked on
+            for (int it = 0; it < kRowsPerItem; ++it) {
+                const int64_t e = start + static_cast<int64_t>(it) * kPanelCols + lane * 8;
+                const f2 v[4] = {mk2(na.x, na.y), mk2(na.z, na.w), mk2(nb.x, nb.y), mk2(nb.z, nb.w)};
+                const int nx = it + 1 < kRowsPerItem ? it + 1 : it;  // past the end: read the last run again
+                na = src[nx * (kPanelCols / 4)];
+                nb = src[nx * (kPanelCols / 4) + 1];
+                const float sc = absmax_pairs_to_block(v);
+                uint32_t w = 0;
+                if (__all_sync(kFull, scale_safe(sc))) {
+                    const f2 r2 = bc2(sc == 0.0f ? 0.0f : __frcp_rn(sc)), ns2 = bc2(-sc);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) v[k] = vn[k];
-        if (it + 1 < kRowsPerItem && wbase + kPanelCols < numel) fetch(wbase + kPanelCols, vn);
-        const float sc = absmax8_bits_to_block(v);
-        if (vec && wbase + kPanelCols <= numel && scale_safe(sc)) {  // full run: packed division, table search
-            const f2 r2 = bc2(sc == 0.0f ? 0.0f : __frcp_rn(sc)), ns2 = bc2(-sc);
-            uint32_t w = 0;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const f2 q = div2_prepared(mk2(v[2 * j], v[2 * j + 1]), r2, ns2);
-                const uint32_t c0 = map ? search_v_closed(q.x) : search_m_lut(q.x, s.mlut);
-                const uint32_t c1 = map ? search_v_closed(q.y) : search_m_lut(q.y, s.mlut);
-                w |= (c0 << (8 * j)) | (c1 << (8 * j + 4));
+                    for (int j = 0; j < 4; ++j) {
+                        const f2 q = div2_prepared(v[j], r2, ns2);
+                        w += (MAP ? search_v_closed(q.x) : search_m_lut(q.x, s.mlut)) << (8 * j);
+                        w += (MAP ? search_v_closed(q.y) : search_m_lut(q.y, s.mlut)) << (8 * j + 4);
+                    }
+                } else {
+                    w = quantize8_pairs_exact(v[0], v[1], v[2], v[3], sc, mid);
+                }
+                *reinterpret_cast<uint32_t*>(codes + (e >> 1)) = w;
+                if ((lane & 15) == 0) scales[e >> 7] = sc;
             }
-            *reinterpret_cast<uint32_t*>(codes + (e >> 1)) = w;
-        } else if (nv) {
-            store_codes(codes, e, nv, vec, quantize8(v, sc, mid, nv));
+            continue;
         }
-        if (nv && (lane & 15) == 0) scales[e >> 7] = sc;
-    }
+        for (int it = 0; it < kRowsPerItem; ++it) {
+            const int64_t wbase = start + static_cast<int64_t>(it) * kPanelCols;
+            if (wbase >= numel) break;
+            const int64_t e = wbase + lane * 8;
+            const int nv = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(8), numel - e)));
+            float v[8];
+            load8_masked<float>(reinterpret_cast<const char*>(x), e, nv, vec, v);
+            const float sc = absmax8_bits_to_block(v);
+            if (nv) store_codes(codes, e, nv, vec, quantize8(v, sc, mid, nv));
+            if (nv && (lane & 15) == 0) scales[e >> 7] = sc;
+        }
     }
 }
 
