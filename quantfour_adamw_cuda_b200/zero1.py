@@ -371,6 +371,9 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
             p.grad = view
 
     def zero_grad(self, set_to_none: bool = False) -> None:
+        """With reduce_grads the gradients are zeroed in the flat buffer and stay attached whatever `set_to_none`
+        says (a gradient set to None would be re-created outside the buffer by the next backward and have to be
+        copied in); without it this is torch's zero_grad."""
         if not self.reduce_grads:
             return super().zero_grad(set_to_none=set_to_none)
         self.flat_grad.zero_()          # the views stay attached: backward keeps accumulating in place
