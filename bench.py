@@ -383,8 +383,8 @@ def main():
         return quantize_micro(args)
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         return single_gpu(args)
-    from quantfour_adamw_cuda_b200 import zero1_bench
-    return zero1_bench.run(args, HP)
+    import bench_zero1
+    return bench_zero1.run(args, HP)
 
 
 if __name__ == "__main__":

@@ -12,8 +12,8 @@ import time
 import torch
 import torch.distributed as dist
 
-from . import shapes as S
-from .zero1 import ShardedFourBitAdamW
+from quantfour_adamw_cuda_b200 import shapes as S
+from quantfour_adamw_cuda_b200.zero1 import ShardedFourBitAdamW
 
 
 def _max_over_ranks(x: float, dev) -> float:
@@ -139,7 +139,7 @@ def run(args, hp) -> None:
     shard_elements, flat_total = opt.layout.shard, opt.layout.total
     # kernels of this library per step on this rank: clear / reciprocals / commit, plus one pre and one main kernel
     # per mapping that has work (whole-row pieces with a column count that is a multiple of 256 take the panel mapping)
-    from .zero1 import RANK1
+    from quantfour_adamw_cuda_b200.zero1 import RANK1
     recs = [st.rec for st in opt.states]
     panel = any(r.kind == RANK1 and not r.partial and r.cols % 256 == 0 for r in recs)
     flat_r1 = any(r.kind == RANK1 and (r.partial or r.cols % 256) for r in recs)

@@ -7,8 +7,10 @@
  * or ATen type in any signature: device pointers, sizes, a device ordinal and a CUDA stream handle.
  * Every function returns a QfStatus; on failure qf_last_error() gives a message for the calling
  * thread.  All launches are asynchronous on the stream that is passed in; nothing synchronises the
- * device except qf_read_status().  The library allocates no device memory: the caller owns every
- * buffer, the workspace included.
+ * device except qf_read_status(), qf_read_status_noalloc() and qf_release_workspace().  (A step call
+ * uploads its descriptor table through one of two pinned host buffers kept per workspace; the host
+ * waits only if the upload of the call before the previous one on that workspace is still in flight.)
+ * The library allocates no device memory: the caller owns every buffer, the workspace included.
  *
  * Data layout (all buffers contiguous, in device memory):
  *   parameters / gradients ... fp32 or bf16, `numel` elements, 16-byte aligned
@@ -30,7 +32,7 @@
 extern "C" {
 #endif
 
-#define QF_ABI_VERSION 3
+#define QF_ABI_VERSION 4
 #define QF_BLOCK 128        /* elements per quantization block (optim/cuda_adamw_kernels.cu:431) */
 #define QF_MAX_HYPERS 16    /* hyper-parameter sets one launch can carry */
 #define QF_MAX_PEERS 15     /* peer copies of the parameter buffer one launch can feed */
@@ -167,12 +169,21 @@ int qf_peer_close(void* base, int device);
  * and clear it. */
 int qf_read_status(void* workspace, int device, void* stream, uint32_t* status);
 
+/* Forget what the library keeps on the host for `workspace` (two pinned staging buffers and two events,
+ * created by the first step call that saw this address): call it before the workspace memory is freed
+ * for good.  Waits for uploads from those buffers that are still in flight.  A host that never calls it
+ * loses nothing but host memory: beyond 64 workspaces the library drops idle entries by itself.  No
+ * counterpart in the reference, whose extension keeps no state. */
+int qf_release_workspace(void* workspace, int device);
+
 /*
  * Single-tensor entry points with the reference's argument order
  * (fused_4bit: cuda_fused_interface.cc:19-25; fused_single_tensor: :49-60).  Scalars are doubles;
  * `step` is the step count after the increment.  In qf_fused_4bit both moments use block-128
  * scales (exp_scale, sq_scale: [ceil(numel/128)]), which is what the reference's signature can
- * express; rank-1 second moments go through qf_step_multi.
+ * express; rank-1 second moments go through qf_step_multi.  These two calls have no workspace and
+ * therefore no status word: a non-finite gradient is not reported (it still propagates into the scales
+ * and the parameters as the arithmetic dictates).  Callers that want the report use qf_step_multi.
  */
 int qf_fused_4bit(void* p, const void* g, void* exp, void* sq, float* exp_scale, float* sq_scale,
                   int64_t numel, int dtype, double beta1, double beta2, double lr, double weight_decay,
@@ -218,10 +229,13 @@ int qf_dequantize_rank1(const uint8_t* codes, const float* row_max, const float*
  *     larger tensors are refused with QF_ERR_BAD_ARG and a message, nothing is launched;
  *   - the first call on a device looks up the device address of the built-in array; make that first
  *     call before any stream capture begins;
- *   - all calls on a device share the one array.  Each call clears what it needs at zero, so leftovers
- *     from the previous call do no harm, but two calls whose kernels overlap on the GPU (different
+ *   - all calls on a device share the one array.  Each call clears what it needs at zero (the status
+ *     word excepted, which accumulates until qf_read_status_noalloc), so leftovers from the previous
+ *     call do no harm, but two calls whose kernels overlap on the GPU (different
  *     streams, or different threads) race on it: keep calls on one device in one stream order;
- *   - the function calls no cudaMalloc / cudaFree / cudaMallocHost and nothing that does.
+ *   - the function calls no cudaMalloc / cudaFree / cudaMallocHost and nothing that does.  Its small
+ *     descriptor goes up with cudaMemcpyAsync from pageable host memory, for which the CUDA runtime may
+ *     make the calling thread wait until the stream has reached the copy;
  * Same arithmetic, same kernels and same in/out buffers as a QF_KIND_RANK1 tensor in qf_step_multi:
  * v_row [rows] and v_col [cols] hold the old maxima on entry and the new ones on return.
  */
@@ -229,6 +243,11 @@ int qf_dequantize_rank1(const uint8_t* codes, const float* row_max, const float*
 int qf_step_rank1_noalloc(void* p, const void* g, void* m_codes, void* v_codes, float* m_scale,
                           float* v_row, float* v_col, int64_t rows, int64_t cols, int dtype,
                           const QfHyper* hyper, int device, void* stream);
+
+/* The status word of qf_step_rank1_noalloc on `device` (QF_STATUS_* bits accumulated over its calls since
+ * the last read): synchronises `stream`, copies the word to *status and clears it.  Allocates nothing
+ * either.  No counterpart in the reference. */
+int qf_read_status_noalloc(int device, void* stream, uint32_t* status);
 
 #ifdef __cplusplus
 }

@@ -9,10 +9,9 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-# QUANTFOUR_B200_LIB may name another build of the same library (e.g. one compiled with different tuning macros).
-LIB_PATH = os.environ.get("QUANTFOUR_B200_LIB") or os.path.join(HERE, "libquantfour_b200.so")
+LIB_PATH = os.path.join(HERE, "libquantfour_b200.so")
 
-QF_ABI_VERSION = 3
+QF_ABI_VERSION = 4
 QF_MAX_HYPERS = 16
 QF_MAX_PEERS = 15
 QF_PEER_HANDLE_BYTES = 64
@@ -53,6 +52,8 @@ _SIGNATURES = {
     "qf_peer_open": (C.c_int, [C.c_char_p, C.c_int, C.POINTER(C.c_void_p)]),
     "qf_peer_close": (C.c_int, [C.c_void_p, C.c_int]),
     "qf_read_status": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.POINTER(C.c_uint32)]),
+    "qf_release_workspace": (C.c_int, [C.c_void_p, C.c_int]),
+    "qf_read_status_noalloc": (C.c_int, [C.c_int, C.c_void_p, C.POINTER(C.c_uint32)]),
     "qf_fused_4bit": (C.c_int, [C.c_void_p] * 6 + [C.c_int64, C.c_int] + _SCALARS + [C.c_int, C.c_void_p]),
     "qf_fused_single_tensor": (C.c_int, [C.c_void_p] * 4 + [C.c_int64, C.c_int] + _SCALARS + [C.c_int, C.c_void_p]),
     "qf_make_hyper": (None, _SCALARS + [C.POINTER(QfHyper)]),

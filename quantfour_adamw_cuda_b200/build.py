@@ -16,7 +16,6 @@ CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libquantfour_b200.so")
 SOURCES = ["qf_api.cu"]
-DEPS = ["qf_api.cu", "qf_kernels.cuh", "qf_device.cuh"]
 
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -35,7 +34,9 @@ def needs_build() -> bool:
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, d) for d in DEPS] + [os.path.join(INCLUDE, "quantfour_b200.h")]
+    # every file of csrc/ is a dependency: a stale library would pass or fail the tests for the wrong source
+    deps = [os.path.join(CSRC, d) for d in sorted(os.listdir(CSRC)) if d.endswith((".cu", ".cuh", ".h"))]
+    deps.append(os.path.join(INCLUDE, "quantfour_b200.h"))
     return any(os.path.getmtime(d) > t for d in deps)
 
 

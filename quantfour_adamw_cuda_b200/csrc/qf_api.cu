@@ -5,6 +5,7 @@
 #include <cstddef>
 #include <cstdio>
 #include <cstring>
+#include <iterator>
 #include <mutex>
 #include <string>
 #include <unordered_map>
@@ -47,8 +48,8 @@ int64_t flat_items(int64_t numel) {
     return (numel + per - 1) / per;
 }
 
-// What the library keeps per workspace: a pair of pinned staging buffers so that the upload of the table
-// never has to wait for the stream.  The table is uploaded on every call: remembering "this table is already
+// What the library keeps per workspace: a pair of pinned staging buffers, so that the upload of the table
+// only ever waits for the upload of the call before the previous one on the same workspace.  The table is uploaded on every call: remembering "this table is already
 // there" would be wrong as soon as the caller recycles the memory (a freed workspace whose address comes back
 // from the allocator zero-filled, with descriptors that happen to be identical), and the copy is a few tens of
 // kilobytes on the launch stream.
@@ -60,6 +61,32 @@ struct WsCache {
 };
 std::mutex g_mu;
 std::unordered_map<uint64_t, WsCache> g_cache;
+constexpr size_t kMaxCachedWorkspaces = 64;  // beyond this many, entries whose uploads have finished are dropped
+
+uint64_t cache_key(int device, const void* workspace) {
+    return (static_cast<uint64_t>(device) << 56) ^ reinterpret_cast<uint64_t>(workspace);
+}
+// Frees the staging buffers of one entry; waits for its uploads first when `wait`, else gives up (false) while one
+// is still in flight.
+bool drop_cache_entry(WsCache& c, bool wait) {
+    for (int k = 0; k < 2; ++k) {
+        if (!c.ev[k]) continue;
+        if (wait)
+            (void)cudaEventSynchronize(c.ev[k]);
+        else if (cudaEventQuery(c.ev[k]) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return false;
+        }
+    }
+    for (int k = 0; k < 2; ++k) {
+        if (c.pinned[k]) (void)cudaFreeHost(c.pinned[k]);
+        if (c.ev[k]) (void)cudaEventDestroy(c.ev[k]);
+        c.pinned[k] = nullptr;
+        c.ev[k] = nullptr;
+    }
+    c.cap = 0;
+    return true;
+}
 
 enum { kMainPanel = 0, kMainFlat = 1, kPrePanel = 2, kPreFlat = 3 };
 struct Plan {
@@ -172,7 +199,13 @@ int build_plan(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* wor
 
     const size_t bytes = table_bytes(n);
     std::lock_guard<std::mutex> lock(g_mu);
-    WsCache& c = g_cache[(static_cast<uint64_t>(device) << 56) ^ reinterpret_cast<uint64_t>(workspace)];
+    const uint64_t key = cache_key(device, workspace);
+    if (g_cache.size() >= kMaxCachedWorkspaces && g_cache.find(key) == g_cache.end()) {
+        // a host that keeps handing in new workspace addresses: forget the entries that are idle
+        for (auto it = g_cache.begin(); it != g_cache.end();)
+            it = drop_cache_entry(it->second, false) ? g_cache.erase(it) : std::next(it);
+    }
+    WsCache& c = g_cache[key];
     if (c.cap < bytes) {
         for (int k = 0; k < 2; ++k) {
             if (c.pinned[k]) cudaFreeHost(c.pinned[k]);
@@ -200,7 +233,7 @@ int grid_for(int64_t items, unsigned* grid) {
     return QF_OK;
 }
 
-// Grid of a multi-tensor kernel: QF_GRID_WAVES waves of CTAs (16 measured best: CTAs live long enough to amortise
+// Grid of a multi-tensor kernel: kGridWaves waves of CTAs (16 measured best: CTAs live long enough to amortise
 // their table set-up, yet the tail stays short), never more than there is work; warps stride over the items.
 int sm_count() {
     static int cached[64] = {};
@@ -212,10 +245,8 @@ int sm_count() {
     }
     return cached[dev];
 }
-#ifndef QF_GRID_WAVES
-#define QF_GRID_WAVES 16
-#endif
-unsigned persistent_grid(int64_t items, int per_sm, int waves = QF_GRID_WAVES) {
+constexpr int kGridWaves = 16;
+unsigned persistent_grid(int64_t items, int per_sm, int waves = kGridWaves) {
     const int64_t ctas = (items + qf::kWarpsPerCta - 1) / qf::kWarpsPerCta;
     const int64_t cap = static_cast<int64_t>(sm_count()) * per_sm * waves;
     return static_cast<unsigned>(ctas < cap ? ctas : cap);
@@ -229,7 +260,7 @@ template <bool SCALE>
 int launch_pre_panel(const Plan& pl, const qf::HyperPack& hp, cudaStream_t stream) {
     const int dyn = qf::pre_dyn_smem(pl.any_f32_panel);
     QF_CUDA(cudaFuncSetAttribute(qf::step_pre_kernel<true, SCALE>, cudaFuncAttributeMaxDynamicSharedMemorySize, qf::pre_dyn_smem(true)));
-    qf::step_pre_kernel<true, SCALE><<<persistent_grid(pl.items[kPrePanel], QF_PRE_MIN_CTAS), qf::kThreads, dyn, stream>>>(
+    qf::step_pre_kernel<true, SCALE><<<persistent_grid(pl.items[kPrePanel], qf::kPreMinCtas), qf::kThreads, dyn, stream>>>(
         pl.d_tensors, pl.d_base[kPrePanel], pl.n, hp, dyn / qf::kWarpsPerCta, pl.d_status);
     return QF_OK;
 }
@@ -243,7 +274,7 @@ int launch_pre(const Plan& pl, const qf::HyperPack& hp, int n_hypers, cudaStream
         if (int rc = scaled ? launch_pre_panel<true>(pl, hp, stream) : launch_pre_panel<false>(pl, hp, stream)) return rc;
     }
     if (pl.items[kPreFlat])
-        qf::step_pre_kernel<false><<<persistent_grid(pl.items[kPreFlat], QF_PRE_MIN_CTAS), qf::kThreads, 0, stream>>>(
+        qf::step_pre_kernel<false><<<persistent_grid(pl.items[kPreFlat], qf::kPreMinCtas), qf::kThreads, 0, stream>>>(
             pl.d_tensors, pl.d_base[kPreFlat], pl.n, hp, 0, pl.d_status);
     QF_CUDA(cudaGetLastError());
     return QF_OK;
@@ -255,7 +286,7 @@ int launch_main_panel(const Plan& pl, const qf::HyperPack& hp, const qf::PushPac
     const int ring = qf::kStages * (pl.any_f32_panel ? qf::kRowBytesF32 : qf::kRowBytesBf16);
     QF_CUDA(cudaFuncSetAttribute(qf::step_main_kernel<true, PUSH, BC1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  qf::main_dyn_smem(true)));
-    qf::step_main_kernel<true, PUSH, BC1><<<persistent_grid(pl.items[kMainPanel], QF_MAIN_MIN_CTAS), qf::kThreads, dyn, stream>>>(
+    qf::step_main_kernel<true, PUSH, BC1><<<persistent_grid(pl.items[kMainPanel], qf::kMainMinCtas), qf::kThreads, dyn, stream>>>(
         pl.d_tensors, pl.d_base[kMainPanel], pl.n, hp, ring, pl.d_status, pp);
     return QF_OK;
 }
@@ -269,7 +300,7 @@ int launch_main_kernels(const Plan& pl, const qf::HyperPack& hp, const qf::PushP
             return rc;
     }
     if (pl.items[kMainFlat])
-        qf::step_main_kernel<false, PUSH><<<persistent_grid(pl.items[kMainFlat], QF_MAIN_MIN_CTAS), qf::kThreads, 0, stream>>>(
+        qf::step_main_kernel<false, PUSH><<<persistent_grid(pl.items[kMainFlat], qf::kMainMinCtas), qf::kThreads, 0, stream>>>(
             pl.d_tensors, pl.d_base[kMainFlat], pl.n, hp, 0, pl.d_status, pp);
     return QF_OK;
 }
@@ -491,6 +522,18 @@ int qf_read_status(void* workspace, int device, void* stream, uint32_t* status) 
     return QF_OK;
 }
 
+int qf_release_workspace(void* workspace, int device) {
+    g_err[0] = 0;
+    if (!workspace) return QF_OK;
+    QF_CUDA(cudaSetDevice(device));
+    std::lock_guard<std::mutex> lock(g_mu);
+    auto it = g_cache.find(cache_key(device, workspace));
+    if (it == g_cache.end()) return QF_OK;
+    drop_cache_entry(it->second, true);
+    g_cache.erase(it);
+    return QF_OK;
+}
+
 int qf_fused_4bit(void* p, const void* g, void* exp, void* sq, float* exp_scale, float* sq_scale, int64_t numel,
                   int dtype, double beta1, double beta2, double lr, double weight_decay, double eps, double step,
                   int device, void* stream) {
@@ -499,6 +542,8 @@ int qf_fused_4bit(void* p, const void* g, void* exp, void* sq, float* exp_scale,
     if (numel < 0) return fail(QF_ERR_BAD_ARG, "negative numel");
     if (numel == 0) return QF_OK;
     if (!p || !g || !exp || !sq || !exp_scale || !sq_scale) return fail(QF_ERR_BAD_ARG, "null pointer");
+    if (!aligned(p, dtype == QF_BF16 ? 2 : 4) || !aligned(g, dtype == QF_BF16 ? 2 : 4) || !aligned(exp_scale, 4) || !aligned(sq_scale, 4))
+        return fail(QF_ERR_BAD_ARG, "qf_fused_4bit: p / g not element-aligned or scales not 4-byte aligned");
     QF_CUDA(cudaSetDevice(device));
     qf::DevTensor t;
     memset(&t, 0, sizeof t);
@@ -528,6 +573,8 @@ int qf_fused_single_tensor(void* p, const void* g, float* exp_avg, float* exp_av
     if (numel < 0) return fail(QF_ERR_BAD_ARG, "negative numel");
     if (numel == 0) return QF_OK;
     if (!p || !g || !exp_avg || !exp_avg_sq) return fail(QF_ERR_BAD_ARG, "null pointer");
+    if (!aligned(p, dtype == QF_BF16 ? 2 : 4) || !aligned(g, dtype == QF_BF16 ? 2 : 4) || !aligned(exp_avg, 4) || !aligned(exp_avg_sq, 4))
+        return fail(QF_ERR_BAD_ARG, "qf_fused_single_tensor: p / g not element-aligned or moments not 4-byte aligned");
     QF_CUDA(cudaSetDevice(device));
     qf::DevTensor t;
     memset(&t, 0, sizeof t);
@@ -553,6 +600,7 @@ int qf_quantize_block(const float* x, int64_t numel, int map, uint8_t* codes, fl
     if (map != 0 && map != 1) return fail(QF_ERR_BAD_ARG, "map must be 0 or 1");
     if (numel == 0) return QF_OK;
     if (!scales) return fail(QF_ERR_BAD_ARG, "scales is null");
+    if (!aligned(x, 4) || !aligned(scales, 4)) return fail(QF_ERR_BAD_ARG, "qf_quantize_block: x / scales not 4-byte aligned");
     QF_CUDA(cudaSetDevice(device));
     const int vec = aligned(x, 16) && aligned(codes, 4);
     const unsigned grid = persistent_grid(flat_items(numel), 8, 2);
@@ -571,6 +619,7 @@ int qf_dequantize_block(const uint8_t* codes, const float* scales, int64_t numel
     if (map != 0 && map != 1) return fail(QF_ERR_BAD_ARG, "map must be 0 or 1");
     if (numel == 0) return QF_OK;
     if (!scales) return fail(QF_ERR_BAD_ARG, "scales is null");
+    if (!aligned(out, 4) || !aligned(scales, 4)) return fail(QF_ERR_BAD_ARG, "qf_dequantize_block: out / scales not 4-byte aligned");
     QF_CUDA(cudaSetDevice(device));
     const int vec = aligned(out, 16) && aligned(codes, 4);
     qf::dequantize_block_kernel<<<flat_grid(numel), qf::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(codes, scales, numel,
@@ -586,6 +635,8 @@ int qf_quantize_rank1(const float* v, int64_t rows, int64_t cols, uint8_t* codes
     const int64_t numel = rows * cols;
     if (numel == 0) return QF_OK;
     if (!v || !codes || !row_max || !col_max) return fail(QF_ERR_BAD_ARG, "null pointer");
+    if (!aligned(v, 4) || !aligned(row_max, 4) || !aligned(col_max, 4))
+        return fail(QF_ERR_BAD_ARG, "qf_quantize_rank1: v / row_max / col_max not 4-byte aligned");
     QF_CUDA(cudaSetDevice(device));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     QF_CUDA(cudaMemsetAsync(row_max, 0, sizeof(float) * rows, st));
@@ -614,6 +665,8 @@ int qf_dequantize_rank1(const uint8_t* codes, const float* row_max, const float*
     const int64_t numel = rows * cols;
     if (numel == 0) return QF_OK;
     if (!codes || !row_max || !col_max || !out) return fail(QF_ERR_BAD_ARG, "null pointer");
+    if (!aligned(out, 4) || !aligned(row_max, 4) || !aligned(col_max, 4))
+        return fail(QF_ERR_BAD_ARG, "qf_dequantize_rank1: out / row_max / col_max not 4-byte aligned");
     QF_CUDA(cudaSetDevice(device));
     const int vec = aligned(out, 16) && aligned(codes, 4);
     if (vec && cols % qf::kPanelCols == 0 && aligned(col_max, 16)) {
@@ -724,8 +777,11 @@ int qf_step_rank1_noalloc(void* p, const void* g, void* m_codes, void* v_codes, 
     h.base[kPrePanel][1] = panel ? pre_items : 0;
     h.base[kPreFlat][1] = panel ? 0 : pre_items;
     // The header goes up from this stack frame; a copy from pageable memory returns once the source has
-    // been staged, so the frame may die afterwards.  The status word is cleared along with it.
-    QF_CUDA(cudaMemcpyAsync(scratch, &h, sizeof h, cudaMemcpyHostToDevice, st));
+    // been staged (for which the runtime may make the host wait for earlier work of the stream), so the frame
+    // may die afterwards.  The status words ahead of the tensor record are not part of the copy: they
+    // accumulate until qf_read_status_noalloc reads and clears them.
+    QF_CUDA(cudaMemcpyAsync(scratch + offsetof(Header, t), reinterpret_cast<const char*>(&h) + offsetof(Header, t),
+                            sizeof h - offsetof(Header, t), cudaMemcpyHostToDevice, st));
 
     Plan pl;
     pl.n = 1;
@@ -742,6 +798,19 @@ int qf_step_rank1_noalloc(void* p, const void* g, void* m_codes, void* v_codes, 
     hp.h[0] = widen_hyper(*hyper);
     if (int rc = launch_pre(pl, hp, 1, st)) return rc;   // clears the new maxima first: the array keeps the last call's
     return launch_main(pl, hp, 1, st);
+}
+
+int qf_read_status_noalloc(int device, void* stream, uint32_t* status) {
+    g_err[0] = 0;
+    if (!status) return fail(QF_ERR_BAD_ARG, "status is null");
+    QF_CUDA(cudaSetDevice(device));
+    unsigned char* scratch = nullptr;
+    if (int rc = noalloc_scratch(device, &scratch)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    QF_CUDA(cudaMemcpyAsync(status, scratch, sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
+    QF_CUDA(cudaMemsetAsync(scratch, 0, sizeof(uint32_t), st));
+    QF_CUDA(cudaStreamSynchronize(st));
+    return QF_OK;
 }
 
 }  // extern "C"

@@ -173,8 +173,7 @@ __device__ __forceinline__ f2 pair_lookup(const float2* tab, uint32_t w, int j) 
 }
 
 __device__ __forceinline__ uint32_t search_m_lut(float x, const LutEntry* lut) {
-    const uint32_t b = __float_as_uint(x);
-    const LutEntry e = *reinterpret_cast<const LutEntry*>(reinterpret_cast<const char*>(lut) + ((b >> 18) & 0x3ff8u));
+    const LutEntry e = lut[__float_as_uint(x) >> 21];
     return e.base + (__uint_as_float(e.thr) < x ? 1u : 0u);
 }
 
@@ -189,6 +188,39 @@ __device__ __forceinline__ uint32_t code_from_y(float y) {
     return CLAMP ? min(c, 15u) : c;
 }
 __device__ __forceinline__ uint32_t search_v_closed(float x) { return code_from_y(__fmaf_rn(x, 16.0f, -1.5f)); }
+
+// ---- integer helpers that compile to one instruction each --------------------------------------------------
+// Two integers saturated to 0..15 become the low byte (hi in bits 7..4, lo in bits 3..0) of the result, above it
+// the low 24 bits of c: four of these in a row pack eight codes, last byte first.  A negative input gives 0, so a
+// code taken by rounding up 16 x - 1.5 needs no lower clamp.
+__device__ __forceinline__ uint32_t pack_u4(int hi, int lo, uint32_t c) {
+    uint32_t d;
+    asm("cvt.pack.sat.u4.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(c));
+    return d;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+// Byte j of w, zero-extended.
+__device__ __forceinline__ uint32_t byte_of(uint32_t w, int j) {
+    return j == 0 ? (w & 0xffu) : j == 3 ? (w >> 24) : prmt(w, 0u, 0x4440u + j);
+}
+// The two bf16 values of a word as floats (low half first): byte permutes, which keep the shift off the
+// multiply-add pipe where the compiler would otherwise place it.
+__device__ __forceinline__ f2 widen_bf16x2(uint32_t w) {
+    return mk2(__uint_as_float(prmt(w, 0u, 0x1044u)), __uint_as_float(prmt(w, 0u, 0x3244u)));
+}
+// ceil(y) as a signed integer (saturating; NaN gives 0).
+__device__ __forceinline__ int ceil_s32(float y) {
+    int c;
+    asm("cvt.rpi.s32.f32 %0, %1;" : "=r"(c) : "f"(y));
+    return c;
+}
+// The pair table entry of byte j of a word of eight codes, and the first-moment code of x, both with the plain
+// index (the scaling by the entry size folds into the shared-memory address).
+__device__ __forceinline__ f2 pair_entry(const float2* tab, uint32_t w, int j) { return tab[byte_of(w, j)]; }
 
 // A scale the fast division sequences may be used with.
 __device__ __forceinline__ bool scale_safe(float s) { return s == 0.0f || (s >= 0x1p-90f && s <= 0x1p100f); }
@@ -296,17 +328,29 @@ __device__ __forceinline__ uint32_t quantize_m8(const f2 (&m)[4], float scale, c
 }
 
 // Max of |x| over the 128-element block a lane's 8 values belong to (16 lanes), by redux instructions on the
-// bit patterns (non-negative floats order like unsigned integers).
-__device__ __forceinline__ float absmax_pairs_to_block(const f2 (&m)[4]) {
-    float a = fmaxf(fmaxf(fabsf(m[0].x), fabsf(m[0].y)), fmaxf(fabsf(m[1].x), fabsf(m[1].y)));
-    a = fmaxf(a, fmaxf(fmaxf(fabsf(m[2].x), fabsf(m[2].y)), fmaxf(fabsf(m[3].x), fabsf(m[3].y))));
-    // two full-warp reductions, each over one half's values (the other half contributes 0): a reduction under
-    // a half-warp mask is compiled into a guarded collective with its own branches and warp syncs
+// bit patterns (non-negative floats order like unsigned integers).  Two full-warp reductions, each over one half's
+// values (the other half contributes 0): a reduction under a half-warp mask is compiled into a guarded collective
+// with its own branches and warp syncs.
+__device__ __forceinline__ float block_max_of_lane_max(uint32_t bits) {
     const bool hi = threadIdx.x & 16;
-    const uint32_t bits = __float_as_uint(a);
     const uint32_t lo_max = __reduce_max_sync(kFull, hi ? 0u : bits);
     const uint32_t hi_max = __reduce_max_sync(kFull, hi ? bits : 0u);
     return __uint_as_float(hi ? hi_max : lo_max);
+}
+// The lane's own maximum through fmaxf, which returns the other operand when one is a NaN: only for callers whose
+// values cannot be NaN (the panel loop: a non-finite gradient or scale sends its row down the exact path first).
+__device__ __forceinline__ float absmax_pairs_to_block(const f2 (&m)[4]) {
+    float a = fmaxf(fmaxf(fabsf(m[0].x), fabsf(m[0].y)), fmaxf(fabsf(m[1].x), fabsf(m[1].y)));
+    a = fmaxf(a, fmaxf(fmaxf(fabsf(m[2].x), fabsf(m[2].y)), fmaxf(fabsf(m[3].x), fabsf(m[3].y))));
+    return block_max_of_lane_max(__float_as_uint(a));
+}
+// The same on bit patterns throughout: a NaN has the largest pattern and survives, as it does in the exact path
+// (absmax8_bits_to_block) and in the reference's abs().max().
+__device__ __forceinline__ float absmax_pairs_to_block_nan(const f2 (&m)[4]) {
+    uint32_t a = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) a = max(a, max(absbits(m[j].x), absbits(m[j].y)));
+    return block_max_of_lane_max(a);
 }
 
 // ---- cp.async helpers (per-lane asynchronous copies global -> shared) -------------------------------------
@@ -482,25 +526,51 @@ __device__ __noinline__ void main_panel_row_exact(const DevTensor* tp, int64_t e
 }
 
 // ---- asynchronous staging of the rows of a panel ---------------------------------------------------------
-// Each lane copies its own 16-byte pieces of p and g and its two code words of the rows ahead into a
-// per-warp ring in shared memory with cp.async and reads them back when their row comes up.  A lane only
-// ever reads what it copied itself, so the ring needs no barrier: cp.async.wait_group orders a lane's
-// copies with its own reads.  One row ahead per warp is enough at two CTAs per SM (deeper rings measured
-// slower: they take shared memory away from L1) and costs no registers.  The per-lane column maxima (old, new,
-// reciprocal of new) sit in shared memory as well and are fetched pair by pair: registers are the scarce
-// resource of this kernel.
+// Each lane copies its own 16-byte pieces of p and g and its two code words of the row ahead into one of two
+// per-warp slots in shared memory with cp.async and reads them back when their row comes up.  A lane only
+// ever reads what it copied itself, so the slots need no barrier: cp.async.wait_group orders a lane's
+// copies with its own reads.  One row ahead per warp is enough at two CTAs per SM (a third slot measured
+// slower, and so did bulk copies with an mbarrier per slot: four 128..512-byte requests per row and warp are too
+// small for the copy engine).  The per-lane column maxima (old, new, reciprocal of new) sit in shared memory as
+// well and are fetched pair by pair: registers are the scarce resource of this kernel (keeping them in registers
+// measured 8 % slower at 128 registers per thread).
 constexpr int kStages = 2;                             // this row and the next one
 constexpr int kRowBytesBf16 = 32 * (2 * 16 + 8);       // staged bytes of one row of a panel, bf16 parameters
 constexpr int kRowBytesF32 = 32 * (2 * 2 * 16 + 8);    // the same for fp32 parameters
 constexpr int kColBytes = 3 * 4 * 32 * 8;              // per warp: old / new / reciprocal column maxima of its 256 columns
-// Dynamic shared memory of the panel kernel: per warp a ring of kStages rows plus the column block.  The host
-// sizes the ring for fp32 rows only when the launch holds an fp32 panel tensor: less shared memory leaves more
-// L1 to the CTA, which the measurements reward.
+// Dynamic shared memory of the panel kernel: per warp the two slots plus the column block.  The host sizes the
+// slots for fp32 rows only when the launch holds an fp32 panel tensor: less shared memory leaves more L1 to the
+// CTA, which the measurements reward.
 constexpr int main_dyn_smem(bool any_f32) { return kWarpsPerCta * (kStages * (any_f32 ? kRowBytesF32 : kRowBytesBf16) + kColBytes); }
 
+// The AdamW update of two elements inside the panel loop (second moment at least 2^-94, see adamw_pair).  P1: the
+// two divisions of the parameter update with one residual correction (div2_prepared1 says what that means); taken for
+// bf16 parameters only.  BC1: sqrt(1 - beta2^t) has rounded to 1, the division by it is left out.
+template <bool P1, bool BC1>
+__device__ __forceinline__ void adamw_pair_panel(f2& p, f2 g, f2& m, f2& v, const Hyper2& h) {
+    const f2 p1 = fma2(p, h.decay, bc2(0.0f));            // not a packed multiply: see adamw_pair
+    m = fma2(h.w1, add2(g, neg2(m)), m);                   // m + w1 * (g - m)
+    v = fma2(mul2(h.w2, g), g, mul2(h.beta2, v));          // beta2 * v + (w2 * g) * g
+    const f2 s = sqrt2<false>(v);
+    const f2 den = add2(BC1 ? s : div2_prepared_n<P1>(s, h.rb, h.nb), h.eps);
+    const f2 a = mul2(h.nstep, m);
+    p = add2(p1, P1 ? div2_1(a, den) : div2(a, den));
+}
+
+// Second pass over one item of a rank-1 panel: 64 rows of 256 columns.
+//
+// The hot loop holds no call and stores nothing of a row before it knows that the whole row could take the packed
+// arithmetic: the row and column scalars inside the range of the division sequences (the pass that stored the
+// reciprocals wrote NaN where an old or a new maximum is not), old maxima above zero (a zero one, as on the first
+// step, lets the second moment fall below the range of the unchecked square root), the old block scale finite and
+// the new one zero or inside the range.  A row that fails leaves the loop untouched and is redone by
+// main_panel_row_exact from its unmodified inputs, after which the hot loop starts again behind it.  Rows go in
+// pairs so that the two staging slots are compile-time offsets and the per-row scalars alternate between two sets of
+// registers; an odd last row of an item takes the exact path as well.
 template <typename T, bool PUSH, bool BC1>
 __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, const HyperDev& hd, const Smem& s,
                                            char* stage, int ring_bytes, uint32_t* status, const PushPack* push) {
+    constexpr bool BF16 = std::is_same<T, __nv_bfloat16>::value;
     const DevTensor t = *tp;
     const int lane = threadIdx.x & 31;
     const int band = static_cast<int>(li / t.panels);
@@ -515,26 +585,21 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
     constexpr int kArr = NV * 512;     // bytes of one staged array of one row
     constexpr int kRowBytes = 2 * kArr + 256;
     static_assert(kRowBytes == (NV == 1 ? kRowBytesBf16 : kRowBytesF32), "staged row size");
-    // Element offsets inside the tensor fit 32 bits (the host gives larger tensors the flat mapping), so a
-    // row costs one 32-bit add per running offset and one widening add per address.
+    static_assert(kStages == 2, "the loop below stages exactly one row ahead and alternates between two slots");
+    // Element offsets inside the tensor fit 32 bits (the host gives larger tensors the flat mapping).
     const uint32_t cols = static_cast<uint32_t>(t.cols);
-    static_assert(kStages == 2, "the loop below stages exactly one row ahead and flips between two slots");
-    auto issue = [&](uint32_t e, uint32_t slot_off) {
-        char* base = stage + slot_off;
+    char* const lane_vec = stage + lane * 16;             // this lane's 16-byte pieces of p (then g) in slot 0
+    char* const lane_codes = stage + 2 * kArr + lane * 4;  // its first-moment (then second-moment) code word in slot 0
+    auto issue = [&](uint32_t e, int slot_off) {
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
-            cp_async16(base + (v * 32 + lane) * 16, t.p + static_cast<size_t>(e) * sizeof(T) + v * 16);
-            cp_async16(base + kArr + (v * 32 + lane) * 16, t.g + static_cast<size_t>(e) * sizeof(T) + v * 16);
+            cp_async16(lane_vec + slot_off + v * 512, t.p + static_cast<size_t>(e) * sizeof(T) + v * 16);
+            cp_async16(lane_vec + slot_off + kArr + v * 512, t.g + static_cast<size_t>(e) * sizeof(T) + v * 16);
         }
-        cp_async4(base + 2 * kArr + lane * 4, mc + (e >> 1));
-        cp_async4(base + 2 * kArr + 128 + lane * 4, vc + (e >> 1));
+        cp_async4(lane_codes + slot_off, mc + (e >> 1));
+        cp_async4(lane_codes + slot_off + 128, vc + (e >> 1));
     };
-    issue(static_cast<uint32_t>(r0) * cols + j0, 0);  // the first row of the item
-    cp_async_commit();
 
-    // The pass that stored the reciprocals wrote NaN where an old or new maximum is outside the range of
-    // the fast sequences.  A zero old maximum (first step, rows never touched) lets v fall below the range
-    // of the unchecked square root, so such rows and columns take the exact path as well.
     float4* colbuf = reinterpret_cast<float4*>(stage + ring_bytes) + lane;  // [old | -new | 1/new][half][lane]
     bool ok = hd.fast;
     {
@@ -565,70 +630,128 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
         o.rrow = ldg_early(t.vrow_rcp + r);
         return o;
     };
-    uint32_t e = static_cast<uint32_t>(r0) * cols + j0;
-    RowScalars sc_next = fetch_scalars(r0, e);
-    uint32_t bad = 0;  // non-finite block scales seen in this item (reported once, at the end)
-    uint32_t off = 0;  // byte offset of the ring slot that holds row r; the other slot is off ^ kRowBytes
-    for (int r = r0; r < r1; ++r, e += cols) {
-        // Stage the next row into the slot the previous row used and fetch its scalars.  Past the end the last
-        // row is staged and fetched again (nobody reads it): cheaper than a branch around the copies.
-        const bool more = r + 1 < r1;
-        const uint32_t e_next = more ? e + cols : e;
-        issue(e_next, off ^ kRowBytes);
-        cp_async_commit();
-        const RowScalars sc = sc_next;
-        sc_next = fetch_scalars(more ? r + 1 : r, e_next);
-        cp_async_wait<1>();  // everything but the newest group has landed: row r is there
-        const char* base = stage + off;
-        off ^= kRowBytes;
-        if (!__all_sync(kFull, col_fast && sc.rrow == sc.rrow && sc.row_old > 0.0f)) {  // the vote tells the compiler it is uniform
-            main_panel_row_exact<T>(tp, e, r, j0, hd, s, status, PUSH ? push : nullptr);
-            continue;
+
+    // One row out of the staging slot at `slot_off`.  False: the row cannot take the packed arithmetic; nothing of
+    // it has been stored.
+    auto row = [&](const RowScalars& sc, uint32_t e, int slot_off) -> bool {
+        // the staged row as it was copied: four words of two bf16 values, or eight floats, per array
+        uint32_t pw[NV * 4], gw[NV * 4];
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            const uint4 a = *reinterpret_cast<const uint4*>(lane_vec + slot_off + v * 512);
+            const uint4 b = *reinterpret_cast<const uint4*>(lane_vec + slot_off + kArr + v * 512);
+            pw[4 * v] = a.x; pw[4 * v + 1] = a.y; pw[4 * v + 2] = a.z; pw[4 * v + 3] = a.w;
+            gw[4 * v] = b.x; gw[4 * v + 1] = b.y; gw[4 * v + 2] = b.z; gw[4 * v + 3] = b.w;
         }
-        Raw8<T> praw, graw;
-        praw.from_shared(base, lane);
-        graw.from_shared(base + kArr, lane);
-        const uint32_t wm = *reinterpret_cast<const uint32_t*>(base + 2 * kArr + lane * 4);
-        const uint32_t wv = *reinterpret_cast<const uint32_t*>(base + 2 * kArr + 128 + lane * 4);
-        float p[8], g[8];
-        praw.widen(p);
-        graw.widen(g);
+        f2 pp[4];
+        const uint32_t wm = *reinterpret_cast<const uint32_t*>(lane_codes + slot_off);
+        const uint32_t wv = *reinterpret_cast<const uint32_t*>(lane_codes + slot_off + 128);
         const f2 ms_old = bc2(sc.ms_old);
         const float row_old = sc.row_old, nrow = -sc.row_new, rrow = sc.rrow;
         f2 m[4];
-        uint32_t wq = 0;
+        int cv[8];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            f2 pp = mk2(p[2 * j], p[2 * j + 1]);
-            m[j] = mul2(pair_lookup(s.qm2, wm, j), ms_old);
-            f2 co, ncn, rcn;
-            {
-                const float4 a = colbuf[(0 * 2 + (j >> 1)) * 32], b = colbuf[(1 * 2 + (j >> 1)) * 32], c = colbuf[(2 * 2 + (j >> 1)) * 32];
-                co = (j & 1) ? mk2(a.z, a.w) : mk2(a.x, a.y);
-                ncn = (j & 1) ? mk2(b.z, b.w) : mk2(b.x, b.y);
-                rcn = (j & 1) ? mk2(c.z, c.w) : mk2(c.x, c.y);
-            }
-            f2 v = mul2(pair_lookup(s.qv2, wv, j), mk2(fminf(row_old, co.x), fminf(row_old, co.y)));
-            adamw_pair<true, BC1>(pp, mk2(g[2 * j], g[2 * j + 1]), m[j], v, h2);
-            p[2 * j] = pp.x;
-            p[2 * j + 1] = pp.y;
+            pp[j] = BF16 ? widen_bf16x2(pw[j]) : mk2(__uint_as_float(pw[(2 * j) % (NV * 4)]), __uint_as_float(pw[(2 * j + 1) % (NV * 4)]));
+            const f2 gg = BF16 ? widen_bf16x2(gw[j]) : mk2(__uint_as_float(gw[(2 * j) % (NV * 4)]), __uint_as_float(gw[(2 * j + 1) % (NV * 4)]));
+            m[j] = mul2(pair_entry(s.qm2, wm, j), ms_old);
+            const float4 a = colbuf[(0 * 2 + (j >> 1)) * 32], b = colbuf[(1 * 2 + (j >> 1)) * 32], c = colbuf[(2 * 2 + (j >> 1)) * 32];
+            const f2 co = (j & 1) ? mk2(a.z, a.w) : mk2(a.x, a.y);
+            const f2 ncn = (j & 1) ? mk2(b.z, b.w) : mk2(b.x, b.y);
+            const f2 rcn = (j & 1) ? mk2(c.z, c.w) : mk2(c.x, c.y);
+            f2 v = mul2(pair_entry(s.qv2, wv, j), mk2(fminf(row_old, co.x), fminf(row_old, co.y)));
+            adamw_pair_panel<BF16, BC1>(pp[j], gg, m[j], v, h2);
             // requantize v: scale = min(row', col') -> -scale = max(-row', -col'), 1/scale = max(1/row', 1/col')
             const f2 nsv = mk2(fmaxf(nrow, ncn.x), fmaxf(nrow, ncn.y));
             const f2 rv = mk2(fmaxf(rrow, rcn.x), fmaxf(rrow, rcn.y));
-            const f2 y = fma2(div2_prepared(v, rv, nsv), bc2(16.0f), bc2(-1.5f));
-            wq += code_from_y<false>(y.x) << (8 * j);
-            wq += code_from_y<false>(y.y) << (8 * j + 4);
+            const f2 y = fma2(div2_prepared1(v, rv, nsv), bc2(16.0f), bc2(-1.5f));
+            cv[2 * j] = ceil_s32(y.x);       // x <= 1 here (the scale is a maximum over values that include v): at most 15
+            cv[2 * j + 1] = ceil_s32(y.y);
         }
-        Elem<T>::store8(t.p, e, p);
-        if (PUSH) push_store8<T>(t.p, e, p, push);
-        *reinterpret_cast<uint32_t*>(vc + (e >> 1)) = wq;
         const float ms_new = absmax_pairs_to_block(m);
-        *reinterpret_cast<uint32_t*>(mc + (e >> 1)) = quantize_m8(m, ms_new, s);
+        const bool row_ok = sc.rrow == sc.rrow && sc.row_old > 0.0f && sc.ms_old < __builtin_huge_valf() && scale_safe(ms_new);
+        if (!__all_sync(kFull, row_ok)) return false;     // the vote also tells the compiler that the branch is uniform
+        uint32_t wmq;
+        {
+            const Recip rc = make_recip(ms_new);  // 0 for an all-zero block: every quotient is 0
+            const f2 r2 = bc2(rc.r), ns2 = bc2(rc.nd);
+            int c[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const f2 q = div2_prepared1(m[j], r2, ns2);
+                c[2 * j] = search_m_lut(q.x, s.mlut);
+                c[2 * j + 1] = search_m_lut(q.y, s.mlut);
+            }
+            wmq = pack_u4(c[1], c[0], pack_u4(c[3], c[2], pack_u4(c[5], c[4], pack_u4(c[7], c[6], 0u))));
+        }
+        const uint32_t wq = pack_u4(cv[1], cv[0], pack_u4(cv[3], cv[2], pack_u4(cv[5], cv[4], pack_u4(cv[7], cv[6], 0u))));
+        if (BF16) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(pp[j].x, pp[j].y);  // nearest even
+                w[j] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            const uint4 out = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4*>(t.p + static_cast<size_t>(e) * 2) = out;
+            if (PUSH) {
+                const int n = push->n;
+                for (int k = 0; k < n; ++k) *reinterpret_cast<uint4*>(t.p + push->delta[k] + static_cast<size_t>(e) * 2) = out;
+            }
+        } else {
+            const float4 o0 = make_float4(pp[0].x, pp[0].y, pp[1].x, pp[1].y), o1 = make_float4(pp[2].x, pp[2].y, pp[3].x, pp[3].y);
+            float4* dst = reinterpret_cast<float4*>(t.p + static_cast<size_t>(e) * 4);
+            dst[0] = o0;
+            dst[1] = o1;
+            if (PUSH) {
+                const int n = push->n;
+                for (int k = 0; k < n; ++k) {
+                    float4* pd = reinterpret_cast<float4*>(t.p + push->delta[k] + static_cast<size_t>(e) * 4);
+                    pd[0] = o0;
+                    pd[1] = o1;
+                }
+            }
+        }
+        *reinterpret_cast<uint32_t*>(vc + (e >> 1)) = wq;
+        *reinterpret_cast<uint32_t*>(mc + (e >> 1)) = wmq;
         if ((lane & 15) == 0) t.ms[e >> 7] = ms_new;
-        bad = max(bad, __float_as_uint(ms_new));  // ms_new >= 0 or NaN: the largest bit pattern seen, checked after the loop
+        return true;
+    };
+
+    int r = r0;
+    while (r < r1) {
+        if (col_fast && r + 1 < r1) {
+            uint32_t e = static_cast<uint32_t>(r) * cols + j0;
+            issue(e, 0);
+            cp_async_commit();
+            RowScalars sa = fetch_scalars(r, e);
+            // rows r (slot 0) and r + 1 (slot 1) per turn; row r is on its way when the turn starts
+            for (; r + 1 < r1; r += 2, e += 2 * cols) {
+                issue(e + cols, kRowBytes);
+                cp_async_commit();
+                const RowScalars sb = fetch_scalars(r + 1, e + cols);
+                cp_async_wait<1>();  // everything but the newest group has landed
+                if (!row(sa, e, 0)) break;
+                // The row behind the pair goes into slot 0.  Past the end the last row is staged and its scalars are
+                // fetched again (nobody reads them): cheaper than a branch around the copies.
+                const bool more = r + 2 < r1;
+                const uint32_t e2 = more ? e + 2 * cols : e + cols;
+                issue(e2, 0);
+                cp_async_commit();
+                sa = fetch_scalars(more ? r + 2 : r + 1, e2);
+                cp_async_wait<1>();
+                if (!row(sb, e + cols, kRowBytes)) {
+                    ++r;
+                    break;
+                }
+            }
+            cp_async_wait<0>();
+        }
+        if (r < r1) {  // cold: this row exactly, from its unmodified inputs
+            main_panel_row_exact<T>(tp, static_cast<uint32_t>(r) * cols + j0, r, j0, hd, s, status, PUSH ? push : nullptr);
+            ++r;
+        }
     }
-    cp_async_wait<0>();
-    if (bad >= 0x7f800000u && (lane & 15) == 0) atomicOr(status, QF_STATUS_NONFINITE);
 }
 
 // =================================================================================================
@@ -842,8 +965,8 @@ __device__ __forceinline__ void main_flat_run_fast(const DevTensor& t, int64_t w
     }
     Elem<T>::store8(t.p, e, p);
     if (push) push_store8<T>(t.p, e, p, push);
-    const float ms_new = absmax_pairs_to_block(m);
-    const float vs_new = absmax_pairs_to_block(v);
+    const float ms_new = absmax_pairs_to_block_nan(m);   // no first pass vouches for these values: a NaN must survive
+    const float vs_new = absmax_pairs_to_block_nan(v);
     *reinterpret_cast<uint32_t*>(mc + (e >> 1)) = quantize_m8(m, ms_new, s);
     uint32_t wq = 0;
     if (scale_safe(vs_new)) {
@@ -898,12 +1021,10 @@ __device__ __forceinline__ void main_flat(const DevTensor* tp, int64_t li, const
 
 // The multi-tensor kernels are persistent: the host launches about as many CTAs as fit on the device and every
 // warp walks the item list with a fixed stride, so the shared-memory tables are filled once per CTA.
-#ifndef QF_PRE_MIN_CTAS
-#define QF_PRE_MIN_CTAS 3
-#endif
+constexpr int kPreMinCtas = 3;   // CTAs per SM the first pass is compiled for (80 registers)
 // SCALE (panel mapping): some hyper-parameter set of the launch carries a gradient scale other than 1.
 template <bool PANEL, bool SCALE = false>
-__global__ void __launch_bounds__(kThreads, QF_PRE_MIN_CTAS)
+__global__ void __launch_bounds__(kThreads, kPreMinCtas)
 step_pre_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict__ base, int n,
                 const __grid_constant__ HyperPack hp, int ring_bytes, uint32_t* status) {
     __shared__ SmemPre s;
@@ -942,13 +1063,11 @@ __device__ __forceinline__ void main_flat_dispatch(const DevTensor* tp, int64_t 
         main_flat<T, QF_KIND_FP32>(tp, li, h, s, status, push);
 }
 
-#ifndef QF_MAIN_MIN_CTAS
-#define QF_MAIN_MIN_CTAS 2
-#endif
+constexpr int kMainMinCtas = 2;  // CTAs per SM the second pass is compiled for (128 registers)
 // PUSH: the launch also stores every updated parameter vector into the peers' buffers named by `pp`.
 // BC1 (panel mapping only): every hyper-parameter set of the launch has bc2s == 1.
 template <bool PANEL, bool PUSH, bool BC1 = false>
-__global__ void __launch_bounds__(kThreads, QF_MAIN_MIN_CTAS)
+__global__ void __launch_bounds__(kThreads, kMainMinCtas)
 step_main_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict__ base, int n,
                  const __grid_constant__ HyperPack hp, int ring_bytes, uint32_t* status,
                  const __grid_constant__ PushPack pp) {
@@ -1052,7 +1171,7 @@ quantize_block_kernel(const float* __restrict__ x, int64_t numel, uint8_t* __res
                 const int nx = it + 1 < kRowsPerItem ? it + 1 : it;  // past the end: read the last run again
                 na = src[nx * (kPanelCols / 4)];
                 nb = src[nx * (kPanelCols / 4) + 1];
-                const float sc = absmax_pairs_to_block(v);
+                const float sc = absmax_pairs_to_block_nan(v);
                 uint32_t w = 0;
                 if (__all_sync(kFull, scale_safe(sc))) {
                     const f2 r2 = bc2(sc == 0.0f ? 0.0f : __frcp_rn(sc)), ns2 = bc2(-sc);

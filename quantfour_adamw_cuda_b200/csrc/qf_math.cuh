@@ -84,6 +84,28 @@ __device__ __forceinline__ f2 div2_prepared(f2 a, f2 r, f2 nd) {
     return fma2(t, r, q);
 }
 
+// The same with one residual correction.  With q0 = RN(a r) and the exact residual t = a - d q0, the value
+// q0 + t r differs from a / d by |a / d - q0| * |1 - d r|, below 2^-45 |a / d| for a reciprocal within two units in
+// the last place; its rounding is therefore the correctly rounded quotient unless a / d lies within that distance of
+// the midpoint of two neighbouring floats.  Quotients of two 24-bit operands come no closer to such a midpoint than
+// about 2^-49 relative, so the exceptions exist but are rare: about one operand pair in 10^7 gets the neighbouring
+// float (tests/cuda/math_check.cu measures the rate).  The step uses this form where the deviation cannot be seen
+// in a result except through a second coincidence:
+//   * requantization: the quotient only selects a code, which changes only if the two candidate quotients also
+//     straddle one of the 15 code boundaries (together about 10^-13 per element; a differing code is then one level
+//     off at an exact near-tie, the case for which the contract allows a fraction of 10^-6);
+//   * the update of bf16 parameters: the quotient enters a sum that is rounded to 8 bits of mantissa (about 10^-13
+//     per element again).  fp32 parameters keep the second correction: there the last place of the quotient is visible.
+__device__ __forceinline__ f2 div2_prepared1(f2 a, f2 r, f2 nd) {
+    const f2 q = mul2(a, r);
+    const f2 t = fma2(nd, q, a);
+    return fma2(t, r, q);
+}
+template <bool ONE>
+__device__ __forceinline__ f2 div2_prepared_n(f2 a, f2 r, f2 nd) {
+    return ONE ? div2_prepared1(a, r, nd) : div2_prepared(a, r, nd);
+}
+
 // a / d for two independent (dividend, divisor) pairs.
 __device__ __forceinline__ f2 div2(f2 a, f2 d) {
     const f2 nd = neg2(d);
@@ -91,6 +113,11 @@ __device__ __forceinline__ f2 div2(f2 a, f2 d) {
     const f2 e = fma2(nd, r0, bc2(1.0f));
     const f2 r = fma2(r0, e, r0);
     return div2_prepared(a, r, nd);
+}
+// The same with the reciprocal as the approximation unit gives it (one unit in the last place) and one correction;
+// see div2_prepared1 for what that costs in accuracy.
+__device__ __forceinline__ f2 div2_1(f2 a, f2 d) {
+    return div2_prepared1(a, mk2(rcp_approx(d.x), rcp_approx(d.y)), neg2(d));
 }
 
 }  // namespace qf

@@ -488,6 +488,13 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
                 pass
         self._peer_bases, self.peer_deltas, self.comm = [], [], "nccl"
 
+    def __del__(self):
+        try:    # peer mappings must not outlive the optimizer; explicit close() stays the orderly way
+            if getattr(self, "_peer_bases", None):
+                self.close()
+        except Exception:  # noqa: BLE001 - interpreter shutdown
+            pass
+
     @property
     def comm_selected(self) -> str:
         """The way parameters were delivered before any close(): "p2p" or "nccl"."""

@@ -72,6 +72,65 @@ __global__ void k_div(uint64_t seed, uint64_t per_thread, int mode, int a_emin, 
     }
 }
 
+// The single-correction forms (div2_prepared1 with r = rcp.rn(d) in mode 0, div2_1 in mode 1): `bad` counts quotients
+// that differ from div.rn, `checked` those that differ by more than one unit in the last place (must stay 0).  With
+// codes != 0 the quotient is additionally turned into a first-moment code (table search) and a second-moment code
+// (closed form) and first_a / first_b count the codes that differ from those of the exact quotient.
+__global__ void k_div1(uint64_t seed, uint64_t per_thread, int mode, int a_emin, int a_emax, int d_emin, int d_emax,
+                       int mant_mode, int codes, Report* r) {
+    __shared__ qf::Smem s;
+    qf::load_smem(s);
+    uint64_t st = seed ^ ((blockIdx.x * (uint64_t)blockDim.x + threadIdx.x) * 0x2545f4914f6cdd1dull);
+    for (uint64_t i = 0; i < per_thread; ++i) {
+        const float d[2] = {rnd_float(st, d_emin, d_emax, false, mant_mode), rnd_float(st, d_emin, d_emax, false, mant_mode)};
+        float a[2] = {rnd_float(st, a_emin, a_emax, true, (int)(i & 1) * mant_mode), rnd_float(st, a_emin, a_emax, true, 0)};
+        if (codes) {
+            a[0] *= d[0];
+            a[1] *= d[1];
+        }
+        const qf::f2 q = mode == 0 ? qf::div2_prepared1(qf::mk2(a[0], a[1]), qf::mk2(__frcp_rn(d[0]), __frcp_rn(d[1])), qf::mk2(-d[0], -d[1]))
+                                   : qf::div2_1(qf::mk2(a[0], a[1]), qf::mk2(d[0], d[1]));
+        const float got[2] = {q.x, q.y};
+        for (int k = 0; k < 2; ++k) {
+            const float want = __fdiv_rn(a[k], d[k]);
+            const int32_t dist = (int32_t)__float_as_uint(got[k]) - (int32_t)__float_as_uint(want);
+            if (dist != 0) atomicAdd(&r->bad, 1ull);
+            if (dist > 1 || dist < -1) atomicAdd(&r->checked, 1ull);
+            if (codes) {
+                if (qf::search_m_lut(got[k], s.mlut) != qf::search_m_lut(want, s.mlut)) atomicAdd(&r->first_a, 1u);
+                if (qf::search_v_closed(fabsf(got[k])) != qf::search_v_closed(fabsf(want))) atomicAdd(&r->first_b, 1u);
+            }
+        }
+    }
+}
+
+// div2_prepared over every mantissa of the dividend (one binade, both signs folded into the index) against 64 divisors
+// spread over a binade: all-zero and all-one mantissas, their neighbours, and an odd-strided walk in between.  The
+// reciprocal comes from make_recip (what the kernels use for a block scale) when recip_mode is 0, from rcp.rn otherwise.
+__global__ void k_div_all_mantissas(int a_exp, int d_exp, int recip_mode, Report* r) {
+    const uint64_t total = (1ull << 23) * 64;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x * 2) {
+        float a[2], d[2];
+        for (int k = 0; k < 2; ++k) {
+            const uint64_t idx = i + (uint64_t)k * gridDim.x * blockDim.x;
+            const uint32_t am = (uint32_t)(idx & 0x7fffffu), dk = (uint32_t)(idx >> 23) & 63u;
+            uint32_t dm = dk < 4 ? dk : dk >= 60 ? 0x7fffffu - (63u - dk) : (dk * 0x20c49bu + 0x1357u) & 0x7fffffu;
+            a[k] = __uint_as_float(((uint32_t)(a_exp + 127) << 23) | am);
+            d[k] = __uint_as_float(((uint32_t)(d_exp + 127) << 23) | dm);
+        }
+        qf::f2 rr, nd = qf::mk2(-d[0], -d[1]);
+        if (recip_mode == 0) {
+            rr = qf::mk2(qf::make_recip(d[0]).r, qf::make_recip(d[1]).r);
+        } else {
+            rr = qf::mk2(__frcp_rn(d[0]), __frcp_rn(d[1]));
+        }
+        const qf::f2 q = qf::div2_prepared(qf::mk2(a[0], a[1]), rr, nd);
+        if (__float_as_uint(q.x) != __float_as_uint(__fdiv_rn(a[0], d[0]))) note(r, __float_as_uint(a[0]), __float_as_uint(d[0]));
+        if (i + (uint64_t)gridDim.x * blockDim.x < total && __float_as_uint(q.y) != __float_as_uint(__fdiv_rn(a[1], d[1])))
+            note(r, __float_as_uint(a[1]), __float_as_uint(d[1]));
+    }
+}
+
 // "round(a*b), then add c" written the way the kernels write it -- fma2(a, b, 0) followed by add2 -- must
 // round twice like mul.rn + add.rn.
 __global__ void k_nofuse(uint64_t seed, uint64_t per_thread, Report* r) {
@@ -150,6 +209,35 @@ int qfc_div(uint64_t seed, uint64_t per_thread, int mode, int a_emin, int a_emax
     Report* d = fresh();
     if (!d) return 1;
     k_div<<<148 * 8, 256>>>(seed, per_thread, mode, a_emin, a_emax, d_emin, d_emax, mant_mode, d);
+    return finish(d, bad, first);
+}
+
+// out[0] = quotients that differ from div.rn, out[1] = by more than one unit, out[2] / out[3] = differing first- /
+// second-moment codes (only with codes != 0)
+int qfc_div1(uint64_t seed, uint64_t per_thread, int mode, int a_emin, int a_emax, int d_emin, int d_emax, int mant_mode,
+             int codes, unsigned long long* out) {
+    Report* d = fresh();
+    if (!d) return 1;
+    k_div1<<<148 * 8, 256>>>(seed, per_thread, mode, a_emin, a_emax, d_emin, d_emax, mant_mode, codes, d);
+    Report h;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(&h, d, sizeof h, cudaMemcpyDeviceToHost);
+    cudaFree(d);
+    if (e != cudaSuccess) {
+        fprintf(stderr, "math_check: %s\n", cudaGetErrorString(e));
+        return 1;
+    }
+    out[0] = h.bad;
+    out[1] = h.checked;
+    out[2] = h.first_a;
+    out[3] = h.first_b;
+    return 0;
+}
+
+int qfc_div_all_mantissas(int a_exp, int d_exp, int recip_mode, unsigned long long* bad, unsigned int* first) {
+    Report* d = fresh();
+    if (!d) return 1;
+    k_div_all_mantissas<<<148 * 8, 256>>>(a_exp, d_exp, recip_mode, d);
     return finish(d, bad, first);
 }
 

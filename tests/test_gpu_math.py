@@ -48,6 +48,43 @@ def test_division_sequences_match_div_rn(mc, mode, a_rng, d_rng, mant_mode):
     assert bad == 0, (first, "of", 2 * per_thread * mc.qfc_threads())
 
 
+@pytest.mark.parametrize("recip_mode", [0, 1], ids=["newton-reciprocal", "rcp.rn"])
+@pytest.mark.parametrize("a_exp,d_exp", [(0, 0), (-3, 0), (-7, 5), (10, -20)])
+def test_prepared_division_on_every_dividend_mantissa_against_64_divisors(mc, recip_mode, a_exp, d_exp):
+    """Structured complement of the random tests: all 2^23 mantissas of the dividend in one binade against 64 divisor
+    mantissas (the extremes, their neighbours and a stride in between), 5.4e8 quotients per case, none may differ."""
+    bad, first = _call(mc.qfc_div_all_mantissas, a_exp, d_exp, recip_mode)
+    assert bad == 0, first
+
+
+@pytest.mark.parametrize("mode", [0, 1], ids=["prepared", "approx-reciprocal"])
+def test_single_correction_division_is_within_one_ulp_and_rarely_off(mc, mode):
+    """The one-correction forms used for the requantize divisions and the bf16 parameter update: never more than one
+    unit off, and off at all in fewer than one quotient in 10^6 (measured: about 10^-7; the rate is printed)."""
+    out = (C.c_ulonglong * 4)()
+    per_thread = 2000
+    assert mc.qfc_div1(C.c_uint64(4321 + mode), C.c_uint64(per_thread), mode, -30, 10, -30, 20, 0, 0, out) == 0
+    n = 2 * per_thread * mc.qfc_threads()
+    print(f"single-correction division, mode {mode}: {out[0]} of {n} quotients differ from div.rn ({out[0] / n:.2e})")
+    assert out[1] == 0
+    assert out[0] / n < 1e-6
+
+
+def test_single_correction_division_changes_no_code(mc):
+    """Codes taken from the one-correction quotient against codes from the exact quotient, |a| <= d as in the step:
+    no code of either map may differ on 1.2e9 random quotients (a difference needs the quotient to sit on a code
+    boundary as well; the estimate is 1e-13 per element)."""
+    out = (C.c_ulonglong * 4)()
+    per_thread = 2000
+    tot = [0, 0, 0]
+    for seed in (7, 8):
+        assert mc.qfc_div1(C.c_uint64(seed), C.c_uint64(per_thread), 0, -9, -1, -60, 60, 0, 1, out) == 0
+        tot = [tot[0] + out[0], tot[1] + out[2], tot[2] + out[3]]
+        assert out[1] == 0
+    print(f"single-correction requantize: {tot[0]} quotients differ, {tot[1]} first-moment and {tot[2]} second-moment codes differ")
+    assert tot[1] == 0 and tot[2] == 0
+
+
 def test_product_taken_as_fma_with_zero_then_add_rounds_twice(mc):
     bad, first = _call(mc.qfc_nofuse, C.c_uint64(99), C.c_uint64(2000))
     assert bad == 0, first

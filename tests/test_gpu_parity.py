@@ -301,6 +301,57 @@ def test_nonfinite_gradient_sets_status_and_does_not_hang():
     assert stepper.status() == 0     # reading clears the word
 
 
+@pytest.mark.parametrize("spec", [((9000,), torch.float32), ((9000,), torch.bfloat16), ((512, 512), torch.bfloat16),
+                                  ((300, 300), torch.float32)],
+                         ids=["block-f32", "block-bf16", "panel-bf16", "rank1-flat-f32"])
+def test_nan_gradient_reaches_the_scales_and_the_status_word(spec):
+    """One NaN gradient after two warm steps: every scale the reference's abs().max() would turn into NaN is NaN here
+    (the packed block maximum must not drop it), the status word reports it, and everything the NaN cannot reach is
+    what the oracle computes.  Codes under a NaN scale are outside the contract (the reference leaves them undefined)."""
+    shape, dt = spec
+    gen, params, ostates, gparams, gstates = _make_problem([spec], seed=11)
+    p, st, gp, gs = params[0], ostates[0], gparams[0], gstates[0]
+    stepper = AbiStepper(gparams, gstates, **HP)
+    for _ in range(2):
+        g = make_grad(shape, dt, gen=gen)
+        TO.step_tensor(p, g, st, *_hp_args())
+        stepper.step([g.to(DEV)])
+    _assert_same(params, ostates, gparams, gstates, "warm")
+    assert stepper.status() == 0
+    g = make_grad(shape, dt, gen=gen)
+    flat = 4321
+    g.view(-1)[flat] = float("nan")
+    TO.step_tensor(p, g, st, *_hp_args())
+    stepper.step([g.to(DEV)])
+    assert stepper.status() & 1
+    n = math.prod(shape)
+    ms, oms = gs.m_scale.cpu(), st.m_scale
+    assert torch.equal(torch.isnan(ms), torch.isnan(oms)) and int(torch.isnan(oms).sum()) == 1
+    assert torch.equal(ms[~torch.isnan(oms)], oms[~torch.isnan(oms)])
+    clean = torch.ones(n, dtype=torch.bool)          # elements whose scales the NaN does not touch
+    clean[flat // 128 * 128:(flat // 128 + 1) * 128] = False
+    if st.kind == "rank1":
+        R, Cc = shape
+        for a, b in ((gs.v_row.cpu(), st.v_row), (gs.v_col.cpu(), st.v_col)):
+            assert torch.equal(torch.isnan(a), torch.isnan(b)) and int(torch.isnan(b).sum()) == 1
+            assert torch.equal(a[~torch.isnan(b)], b[~torch.isnan(b)])
+        grid = clean.view(R, Cc)
+        grid[flat // Cc, :] = False
+        grid[:, flat % Cc] = False
+    else:
+        vs, ovs = gs.v_scale.cpu(), st.v_scale
+        assert torch.equal(torch.isnan(vs), torch.isnan(ovs)) and int(torch.isnan(ovs).sum()) == 1
+        assert torch.equal(vs[~torch.isnan(ovs)], ovs[~torch.isnan(ovs)])
+    cm, om = TO.unpack(gs.m_codes.cpu(), n), TO.unpack(st.m_codes, n)
+    cv, ov = TO.unpack(gs.v_codes.cpu(), n), TO.unpack(st.v_codes, n)
+    assert torch.equal(cm[clean], om[clean]) and torch.equal(cv[clean], ov[clean])
+    pg, po = gp.cpu().view(-1), p.view(-1)
+    assert torch.isnan(pg[flat]) and torch.isnan(po[flat])
+    keep = torch.ones(n, dtype=torch.bool)
+    keep[flat] = False
+    assert torch.equal(pg[keep], po[keep])
+
+
 def test_unaligned_views_take_the_scalar_path():
     """Buffers that are only element-aligned (views at odd offsets) still give oracle results."""
     n = 5003

@@ -45,6 +45,26 @@ def test_argument_errors_are_reported_without_a_gpu(lib):
         _lib.check(1, "x")
 
 
+def test_misaligned_buffers_are_refused_before_anything_is_launched(lib):
+    """The single-tensor and stand-alone entry points promise QF_ERR_BAD_ARG for buffers that are not aligned to
+    their element; the addresses below are never dereferenced (the checks come before any CUDA call)."""
+    A, odd = 0x10000, 0x10002   # 4-byte aligned / not
+    sc = (0.9, 0.999, 1e-3, 0.0, 1e-8, 1.0)
+    assert lib.qf_fused_4bit(odd, A, A, A, A, A, 256, _lib.QF_F32, *sc, 0, None) == 1 and b"aligned" in lib.qf_last_error()
+    assert lib.qf_fused_4bit(A, A, A, A, odd, A, 256, _lib.QF_BF16, *sc, 0, None) == 1 and b"aligned" in lib.qf_last_error()
+    assert lib.qf_fused_4bit(A + 1, A, A, A, A, A, 256, _lib.QF_BF16, *sc, 0, None) == 1
+    assert lib.qf_fused_single_tensor(A, A, odd, A, 256, _lib.QF_F32, *sc, 0, None) == 1 and b"aligned" in lib.qf_last_error()
+    assert lib.qf_quantize_block(odd, 256, 0, A, A, 0, None) == 1 and b"aligned" in lib.qf_last_error()
+    assert lib.qf_dequantize_block(A, odd, 256, 0, A, 0, None) == 1 and b"aligned" in lib.qf_last_error()
+    assert lib.qf_quantize_rank1(A, 16, 16, A, odd, A, 0, None) == 1 and b"aligned" in lib.qf_last_error()
+    assert lib.qf_dequantize_rank1(A, A, odd, 16, 16, A, 0, None) == 1 and b"aligned" in lib.qf_last_error()
+
+
+def test_release_of_nothing_is_not_an_error(lib):
+    assert lib.qf_release_workspace(None, 0) == 0
+    assert lib.qf_read_status_noalloc(0, None, None) == 1 and b"status" in lib.qf_last_error()
+
+
 def test_make_hyper_matches_oracle_and_c_library(lib):
     for step in (1, 2, 3, 10, 1000, 123456):
         h = qf.make_hyper(1e-3, 0.9, 0.999, 1e-8, 0.01, float(step))

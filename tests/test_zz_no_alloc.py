@@ -13,6 +13,7 @@ import pytest
 import torch
 
 from helpers import AbiStepper, GpuState, make_grad
+from oracle import c_oracle as CO
 from oracle import torch_oracle as TO
 from quantfour_adamw_cuda_b200 import _lib
 from quantfour_adamw_cuda_b200.optimizer import make_hyper
@@ -55,6 +56,49 @@ def test_noalloc_step_equals_step_multi_on_two_calls_in_a_row(shape, dtype):
         assert torch.equal(sa.m_codes, sb.m_codes) and torch.equal(sa.v_codes, sb.v_codes), f"step {step}: codes differ"
         assert torch.equal(sa.m_scale, sb.m_scale), f"step {step}: first-moment scales differ"
         assert torch.equal(sa.v_row, sb.v_row) and torch.equal(sa.v_col, sb.v_col), f"step {step}: maxima differ"
+
+
+def _noalloc_status():
+    word = C.c_uint32(0)
+    _lib.check(_lib.lib().qf_read_status_noalloc(0, C.c_void_p(torch.cuda.current_stream().cuda_stream), C.byref(word)),
+               "qf_read_status_noalloc")
+    return word.value
+
+
+def test_noalloc_step_matches_the_oracle_and_takes_no_device_memory():
+    """Directly against the CPU oracle (not only against the other entry point), and the claim in the name: the free
+    device memory the driver reports is the same before and after a call once the first call has been made."""
+    shape, dtype = (256, 512), torch.bfloat16
+    gen = torch.Generator().manual_seed(3)
+    p = (torch.randn(shape, generator=gen) * 0.02).to(dtype)
+    st = TO.TensorState.zeros(shape)
+    gp, gs = p.cuda(), GpuState(st)
+    for step in range(1, 4):
+        g = make_grad(shape, dtype, gen=gen)
+        gg = g.cuda()
+        CO.step_tensor(p, g, st, HP["lr"], *HP["betas"], HP["eps"], HP["weight_decay"])
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        _noalloc_step(gp, gg, gs, step)
+        torch.cuda.synchronize()
+        if step > 1:   # the first call on a device may load the module that holds the built-in array
+            assert torch.cuda.mem_get_info()[0] == free_before
+        assert torch.equal(gp.cpu(), p), f"step {step}: parameters differ from the oracle"
+        assert not any(gs.diff(st).values()), f"step {step}: {gs.diff(st)}"
+    assert _noalloc_status() == 0
+
+
+def test_noalloc_status_word_is_sticky_until_read():
+    shape = (64, 256)
+    p, st = torch.zeros(shape, device="cuda"), GpuState(TO.TensorState.zeros(shape))
+    _noalloc_status()
+    g = torch.full(shape, 1e-3, device="cuda")
+    g[5, 9] = float("nan")
+    _noalloc_step(p, g, st, 1)
+    p2, st2 = torch.zeros(shape, device="cuda"), GpuState(TO.TensorState.zeros(shape))
+    _noalloc_step(p2, torch.full(shape, 1e-3, device="cuda"), st2, 1)   # a clean call in between must not clear the report
+    assert _noalloc_status() & _lib.QF_STATUS_NONFINITE
+    assert _noalloc_status() == 0
 
 
 def test_noalloc_step_refuses_tensors_beyond_its_scratch():
