@@ -37,9 +37,10 @@ from quantfour_adamw_cuda_b200 import shapes as S  # noqa: E402
 
 HP = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes per algorithmic byte of a step, from one ncu capture of the two kernels on the GPT-2-medium-shaped
-# set (dram__bytes_read.sum + dram__bytes_write.sum = 3.729 GB for 2.869 GB algorithmic; the pre pass re-reads
-# gradients and second-moment codes).  Traffic grows in proportion to the elements processed.
+# DRAM bytes per algorithmic byte of a step, from one ncu capture of the two step kernels on the GPT-2-medium-shaped
+# set (dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes; the first pass re-reads gradients and
+# second-moment codes).  Traffic grows in proportion to the elements processed, so the figure for the bench workload
+# is this factor times its algorithmic bytes; the result line says that it is scaled, not captured.
 TRAFFIC_PER_ALGORITHMIC_BYTE = 3.729 / 2.869
 
 
@@ -288,7 +289,7 @@ def single_gpu(args):
     achieved = alg_bytes / (ms_per_step * 1e-3) / 1e9
     out = {
         "metric": "4-bit AdamW step throughput", "value": value, "unit": "Gparams/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload, "tensors": len(shapes), "params": n_params, "param_dtype": "bf16",
                    "start_step": args.start_step, "grad_scale": args.grad_scale,
@@ -298,13 +299,17 @@ def single_gpu(args):
                    "ms_per_step_median": float(np.median(per_step)), "ms_per_step_p10": float(np.percentile(per_step, 10)),
                    "ms_per_step_p90": float(np.percentile(per_step, 90))},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": alg_bytes * TRAFFIC_PER_ALGORITHMIC_BYTE, "traffic_note": "scaled from the ncu capture on the "
-                     "355 M-parameter set (profiles/step_main_pre_kernels_gpt2m.md)",
+                     "traffic": alg_bytes * TRAFFIC_PER_ALGORITHMIC_BYTE,
+                     "traffic_kind": "scaled from an ncu capture of the same kernels on the 355 M-parameter set",
                      "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
                      "algorithmic_bytes_per_step": alg_bytes, "kernels_ms": {"pre": pre_ms, "main": main_ms},
                      "note": "whole step (clear, pre, reciprocals, main panel, main flat, commit: 6 launches) over algorithmic bytes"},
         "e2e": e2e, "gpu_launches": 6 * args.steps, "clocks": clocks,
     }
+    if not args.no_also:
+        del opt, params, grads
+        torch.cuda.empty_cache()
+        out["also"] = also_block(dev, peak)
     if not args.no_cpu:
         v, cores, dt, text = run_cpu(workload, "c", 3, 1)
         out["cpu_baseline"] = {"value": v, "unit": "Gparams/s", "cores": cores, "kind": "port", "sample": text,
@@ -312,13 +317,69 @@ def single_gpu(args):
     print(json.dumps(out))
 
 
-def quantize_micro(args):
-    """Stand-alone quantize / dequantize micro-benchmark: first-moment path on 2^28 fp32 values ~N(0, 1e-3) with 0.1 %
-    of the entries x100 (block-128, dynamic-exponent map), second-moment path on a 16384 x 16384 fp32 matrix of squared
-    N(0, 1e-3) values (rank-1 row / column maxima).  One JSON line; GB/s over the compulsory bytes of each call."""
+def timed_steps(opt, params, grads, steps, dev):
+    """Device time per step over `steps` steps of `opt` with the gradient sets rotated."""
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    ev0.record()
+    for i in range(steps):
+        for p, g in zip(params, grads[i % len(grads)]):
+            p.grad = g
+        opt.step()
+    ev1.record()
+    torch.cuda.synchronize(dev)
+    return ev0.elapsed_time(ev1) / steps
+
+
+def also_block(dev, peak):
+    """The other configurations of the benchmark list on this GPU, outside the timed region of the headline: the
+    single fp32 4096 x 4096 parameter, the stand-alone quantize / dequantize kernels, the GPT-2-medium-shaped list
+    (first step from zero state, and warm), and the Llama-13B-shaped set unsharded."""
     import quantfour_adamw_cuda_b200 as qf
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
+    out = {}
+    # one fp32 4096 x 4096 parameter, 10 steps with fresh gradients (the reference's CPU-runnable case, here on the GPU)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    p = torch.nn.Parameter(torch.randn(4096, 4096, generator=gen, device=dev) * 0.02, requires_grad=False)
+    gs = [[torch.randn(4096, 4096, generator=gen, device=dev) * 1e-3] for _ in range(10)]
+    opt = qf.FourBitAdamW([p], **HP)
+    timed_steps(opt, [p], gs, 10, dev)                      # the ten steps of the configuration (from zero state)
+    ms = timed_steps(opt, [p], gs, 20, dev)                 # the same gradients again, warm
+    nbytes = S.algorithmic_bytes([(4096, 4096)], elem_bytes=4)
+    out["fp32_4096x4096"] = {"ms_per_step": ms, "GBps": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak,
+                             "algorithmic_bytes": nbytes, "note": "fp32 parameter and gradient: 14 bytes per element"}
+    del opt, p, gs
+    # stand-alone quantize / dequantize
+    out["quantize"] = quantize_kernels(dev, peak, steps=20, warmup=3)
+    torch.cuda.empty_cache()
+    # GPT-2-medium-shaped ragged list
+    shapes = S.WORKLOADS["gpt2m"]()
+    params, grads = build_problem(shapes, dev, grad_sets=1)
+    opt = qf.FourBitAdamW(params, **HP)
+    first = timed_steps(opt, params, grads, 1, dev)         # includes state allocation and the exact arithmetic of a zero state
+    timed_steps(opt, params, grads, 3, dev)
+    ms = timed_steps(opt, params, grads, 50, dev)
+    nbytes = S.algorithmic_bytes(shapes)
+    out["gpt2m"] = {"ms_per_step": ms, "first_step_ms": first, "params": S.numel(shapes), "tensors": len(shapes),
+                    "GBps": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak}
+    del opt, params, grads
+    torch.cuda.empty_cache()
+    # Llama-13B-shaped set on one GPU (the sharded runs use it at 2, 4 and 8 GPUs)
+    shapes = S.WORKLOADS["llama13b"]()
+    params, grads = build_problem(shapes, dev, grad_sets=1)
+    opt = qf.FourBitAdamW(params, **HP)
+    timed_steps(opt, params, grads, 4, dev)
+    ms = timed_steps(opt, params, grads, 8, dev)
+    nbytes = S.algorithmic_bytes(shapes)
+    out["llama13b"] = {"ms_per_step": ms, "params": S.numel(shapes), "Gparams_per_s": S.numel(shapes) / ms / 1e6,
+                       "GBps": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak}
+    del opt, params, grads
+    torch.cuda.empty_cache()
+    return out
+
+
+def quantize_kernels(dev, peak, steps, warmup):
+    """Times of the four stand-alone kernels at the sizes of the quantize / dequantize configuration."""
+    import quantfour_adamw_cuda_b200 as qf
     n = 1 << 28
     x = torch.randn(n, generator=torch.Generator(device=dev).manual_seed(0), device=dev) * 1e-3
     x = torch.where(torch.rand(n, generator=torch.Generator(device=dev).manual_seed(1), device=dev) < 1e-3, x * 100, x)
@@ -332,26 +393,39 @@ def quantize_micro(args):
         "quantize_v_rank1": (lambda: qf.quantize_v(v), R * C * 4.5 + 8 * R),
         "dequantize_v_rank1": (lambda: qf.dequantize_v(codes_v, row, col), R * C * 4.5 + 8 * R),
     }
-    peak, peak_kind = measured_peak()
     out = {}
     for name, (fn, nbytes) in cases.items():
-        for _ in range(max(3, args.warmup)):
+        for _ in range(max(3, warmup)):
             fn()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize(dev)
         e0.record()
-        for _ in range(args.steps):
+        for _ in range(steps):
             fn()
         e1.record()
         torch.cuda.synchronize(dev)
-        ms = e0.elapsed_time(e1) / args.steps
+        ms = e0.elapsed_time(e1) / steps
         out[name] = {"ms": ms, "GBps": nbytes / ms / 1e6, "frac_of_peak": nbytes / ms / 1e6 / peak}
+    out["quantize_v_rank1"]["two_read_bound_frac"] = (R * C * 4.5 + 8 * R) / (R * C * 8.5 + 8 * R)
+    out["note"] = ("2^28 fp32 values (block-128, dynamic-exponent map) and a 16384 x 16384 fp32 matrix (rank-1); GB/s over the "
+                   "compulsory bytes of each call; the rank-1 quantize has to read its input twice (maxima, then codes), which "
+                   "caps it at two_read_bound_frac of the peak on this scale; timings include the allocation of the outputs by "
+                   "torch's caching allocator")
+    return out
+
+
+def quantize_micro(args):
+    """Stand-alone quantize / dequantize micro-benchmark: first-moment path on 2^28 fp32 values ~N(0, 1e-3) with 0.1 %
+    of the entries x100 (block-128, dynamic-exponent map), second-moment path on a 16384 x 16384 fp32 matrix of squared
+    N(0, 1e-3) values (rank-1 row / column maxima).  One JSON line; GB/s over the compulsory bytes of each call."""
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peak, peak_kind = measured_peak()
+    out = quantize_kernels(dev, peak, args.steps, args.warmup)
+    note = out.pop("note")
     print(json.dumps({"metric": "stand-alone quantize / dequantize", "unit": "GB/s over compulsory bytes", "n_gpus": 1,
                       "steps": args.steps, "data": "synthetic", "peak": peak, "peak_kind": peak_kind,
-                      "config": {"workload": "quantize", "m": "2^28 fp32", "v": "16384x16384 fp32",
-                                 "note": "the rank-1 quantize has to read its input twice (maxima, then codes): "
-                                         "a perfect implementation shows about 53 % on this scale; timings include the "
-                                         "allocation of the outputs by torch's caching allocator"},
+                      "config": {"workload": "quantize", "m": "2^28 fp32", "v": "16384x16384 fp32", "note": note},
                       "kernels": out}))
 
 
@@ -373,6 +447,7 @@ def main():
                     help="N=1: pass this factor to every timed step (the first pass then rewrites the gradients scaled); "
                          "use a value next to 1, e.g. 1.0000001, so that repeated steps do not drive the data to zero")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-also", action="store_true", help="skip the other configurations reported beside the headline")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":

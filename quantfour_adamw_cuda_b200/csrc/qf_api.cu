@@ -649,8 +649,8 @@ int qf_quantize_rank1(const float* v, int64_t rows, int64_t cols, uint8_t* codes
     if (int rc = grid_for(max_items, &grid)) return rc;
     qf::rank1_max_kernel<<<grid, qf::kThreads, 0, st>>>(v, static_cast<int>(rows), static_cast<int>(cols), row_max, col_max, panel);
     if (panel && aligned(col_max, 16))
-        qf::rank1_codec_panel_kernel<true><<<persistent_grid(items, 8), qf::kThreads, 0, st>>>(v, codes, row_max, col_max, static_cast<int>(rows),
-                                                                                            static_cast<int>(cols), nullptr);
+        qf::rank1_quant_panel_kernel<<<persistent_grid(items, 8), qf::kThreads, 0, st>>>(v, codes, row_max, col_max, static_cast<int>(rows),
+                                                                                      static_cast<int>(cols));
     else
         qf::rank1_codec_kernel<true><<<flat_grid(numel), qf::kThreads, 0, st>>>(v, codes, row_max, col_max, static_cast<int>(rows),
                                                                                static_cast<int>(cols), nullptr, vec);
@@ -671,8 +671,8 @@ int qf_dequantize_rank1(const uint8_t* codes, const float* row_max, const float*
     const int vec = aligned(out, 16) && aligned(codes, 4);
     if (vec && cols % qf::kPanelCols == 0 && aligned(col_max, 16)) {
         const int64_t items = (rows + qf::kRowsPerItem - 1) / qf::kRowsPerItem * (cols / qf::kPanelCols);
-        qf::rank1_codec_panel_kernel<false><<<persistent_grid(items, 8), qf::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-            nullptr, const_cast<uint8_t*>(codes), row_max, col_max, static_cast<int>(rows), static_cast<int>(cols), out);
+        qf::rank1_dequant_panel_kernel<<<persistent_grid(items, 8), qf::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+            codes, row_max, col_max, static_cast<int>(rows), static_cast<int>(cols), out);
     } else {
         qf::rank1_codec_kernel<false><<<flat_grid(numel), qf::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
             nullptr, const_cast<uint8_t*>(codes), row_max, col_max, static_cast<int>(rows), static_cast<int>(cols), out, vec);

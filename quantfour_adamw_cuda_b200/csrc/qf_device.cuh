@@ -175,8 +175,9 @@ struct Raw8<__nv_bfloat16> {
         const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            x[2 * k] = __uint_as_float(w[k] << 16);
-            x[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+            // byte permutes: a plain shift tends to be placed on the multiply-add pipe, which these kernels fill anyway
+            asm("prmt.b32 %0, %1, 0, 0x1044;" : "=f"(x[2 * k]) : "r"(w[k]));
+            asm("prmt.b32 %0, %1, 0, 0x3244;" : "=f"(x[2 * k + 1]) : "r"(w[k]));
         }
     }
 };

@@ -1163,29 +1163,48 @@ quantize_block_kernel(const float* __restrict__ x, int64_t numel, uint8_t* __res
     for (int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5); item < total; item += stride) {
         const int64_t start = item * per_item;
         if (vec && start + per_item <= numel) {  // warp-uniform
-            const float4* src = reinterpret_cast<const float4*>(x + start) + lane * 2;
-            float4 na = src[0], nb = src[1];  // the next run's input is requested before this run is worked on
+            // Lane L takes elements 4L .. 4L+3 of the first and of the second 128-block of a run: each of its two
+            // 128-bit loads is then one of 32 consecutive 16-byte pieces (a load instruction of the warp reads 512
+            // contiguous bytes), and each block maximum is one reduction over the whole warp.
+            const float4* src = reinterpret_cast<const float4*>(x + start) + lane;
+            uint16_t* c16 = reinterpret_cast<uint16_t*>(codes + (start >> 1)) + lane;
+            float* sc_out = scales + (start >> 7);
+            float4 na = src[0], nb = src[32];  // the next run's input is requested before this run is worked on
             for (int it = 0; it < kRowsPerItem; ++it) {
-                const int64_t e = start + static_cast<int64_t>(it) * kPanelCols + lane * 8;
-                const f2 v[4] = {mk2(na.x, na.y), mk2(na.z, na.w), mk2(nb.x, nb.y), mk2(nb.z, nb.w)};
+                const f2 va[2] = {mk2(na.x, na.y), mk2(na.z, na.w)}, vb[2] = {mk2(nb.x, nb.y), mk2(nb.z, nb.w)};
                 const int nx = it + 1 < kRowsPerItem ? it + 1 : it;  // past the end: read the last run again
-                na = src[nx * (kPanelCols / 4)];
-                nb = src[nx * (kPanelCols / 4) + 1];
-                const float sc = absmax_pairs_to_block_nan(v);
-                uint32_t w = 0;
-                if (__all_sync(kFull, scale_safe(sc))) {
-                    const f2 r2 = bc2(sc == 0.0f ? 0.0f : __frcp_rn(sc)), ns2 = bc2(-sc);
+                na = src[nx * 64];
+                nb = src[nx * 64 + 32];
+                // bit patterns, so that a NaN survives the maximum
+                const uint32_t ma = max(max(absbits(va[0].x), absbits(va[0].y)), max(absbits(va[1].x), absbits(va[1].y)));
+                const uint32_t mb = max(max(absbits(vb[0].x), absbits(vb[0].y)), max(absbits(vb[1].x), absbits(vb[1].y)));
+                const float sa = __uint_as_float(__reduce_max_sync(kFull, ma)), sb = __uint_as_float(__reduce_max_sync(kFull, mb));
+                uint32_t wa = 0, wb = 0;
+                if (scale_safe(sa) && scale_safe(sb)) {   // warp-uniform: both are reduction results
+                    const f2 ra = bc2(sa == 0.0f ? 0.0f : __frcp_rn(sa)), nsa = bc2(-sa);
+                    const f2 rb = bc2(sb == 0.0f ? 0.0f : __frcp_rn(sb)), nsb = bc2(-sb);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const f2 q = div2_prepared(v[j], r2, ns2);
-                        w += (MAP ? search_v_closed(q.x) : search_m_lut(q.x, s.mlut)) << (8 * j);
-                        w += (MAP ? search_v_closed(q.y) : search_m_lut(q.y, s.mlut)) << (8 * j + 4);
+                    for (int j = 0; j < 2; ++j) {
+                        const f2 qa = div2_prepared(va[j], ra, nsa), qb = div2_prepared(vb[j], rb, nsb);
+                        wa += (MAP ? search_v_closed(qa.x) : search_m_lut(qa.x, s.mlut)) << (8 * j);
+                        wa += (MAP ? search_v_closed(qa.y) : search_m_lut(qa.y, s.mlut)) << (8 * j + 4);
+                        wb += (MAP ? search_v_closed(qb.x) : search_m_lut(qb.x, s.mlut)) << (8 * j);
+                        wb += (MAP ? search_v_closed(qb.y) : search_m_lut(qb.y, s.mlut)) << (8 * j + 4);
                     }
                 } else {
-                    w = quantize8_pairs_exact(v[0], v[1], v[2], v[3], sc, mid);
+                    const float xa[4] = {va[0].x, va[0].y, va[1].x, va[1].y}, xb[4] = {vb[0].x, vb[0].y, vb[1].x, vb[1].y};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        wa |= search16(scaled(xa[k], sa), mid) << (4 * k);
+                        wb |= search16(scaled(xb[k], sb), mid) << (4 * k);
+                    }
                 }
-                *reinterpret_cast<uint32_t*>(codes + (e >> 1)) = w;
-                if ((lane & 15) == 0) scales[e >> 7] = sc;
+                c16[it * 64] = static_cast<uint16_t>(wa);
+                c16[it * 64 + 32] = static_cast<uint16_t>(wb);
+                if (lane == 0) {
+                    sc_out[2 * it] = sa;
+                    sc_out[2 * it + 1] = sb;
+                }
             }
             continue;
         }
@@ -1203,41 +1222,101 @@ quantize_block_kernel(const float* __restrict__ x, int64_t numel, uint8_t* __res
     }
 }
 
+// How the stand-alone dequantize kernels divide a run of 256 fp32 outputs (1 KB) among the lanes: lane L writes
+// elements 4L .. 4L+3 and 128+4L .. 128+4L+3, so that each of its two 128-bit stores is one of 32 consecutive 16-byte
+// pieces: a store instruction of the warp then covers 512 contiguous bytes.  With 8 consecutive elements per lane the
+// two stores of a lane would sit 32 bytes apart and every instruction would write half of each 32-byte sector.
+// The codes of a lane's two quads are two 16-bit loads (64 contiguous bytes per warp each).
 __global__ void __launch_bounds__(kThreads)
 dequantize_block_kernel(const uint8_t* __restrict__ codes, const float* __restrict__ scales, int64_t numel, int map,
                         float* __restrict__ out, int vec) {
     __shared__ Tables s;
-    load_tables(s);
+    __shared__ float2 pair[256];   // (value of the low nibble, value of the high nibble) of a byte of codes
+    for (int i = threadIdx.x; i < 256; i += blockDim.x)
+        pair[i] = map ? make_float2(c_qv[i & 15], c_qv[i >> 4]) : make_float2(c_qm[i & 15], c_qm[i >> 4]);
+    load_tables(s);  // ends with __syncthreads()
     const float* q = map ? s.qv : s.qm;
     const int lane = threadIdx.x & 31;
     const int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
     const int64_t start = item * (kPanelCols * kRowsPerItem);
-    // the code words and scales of four runs are requested together, then expanded and stored
-    for (int it0 = 0; it0 < kRowsPerItem; it0 += 4) {
-        uint32_t wv[4];
-        float scv[4];
+    if (vec && start + kPanelCols * kRowsPerItem <= numel) {  // warp-uniform: a whole item inside an aligned tensor
+        const uint16_t* c16 = reinterpret_cast<const uint16_t*>(codes + (start >> 1)) + lane;
+        const float* sc = scales + (start >> 7);
+        float4* dst = reinterpret_cast<float4*>(out + start) + lane;
+        // the code halves and scales of four runs are requested together, then expanded and stored
+        for (int it0 = 0; it0 < kRowsPerItem; it0 += 4) {
+            uint32_t wa[4], wb[4];
+            float sa[4], sb[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int64_t e = start + static_cast<int64_t>(it0 + i) * kPanelCols + lane * 8;
-            wv[i] = 0;
-            scv[i] = 0.0f;
-            if (e < numel) {
-                wv[i] = load_codes(codes, e, static_cast<int>(min(static_cast<int64_t>(8), numel - e)), vec);
-                scv[i] = __ldg(scales + (e >> 7));
+            for (int i = 0; i < 4; ++i) {
+                wa[i] = __ldg(c16 + (it0 + i) * 64);
+                wb[i] = __ldg(c16 + (it0 + i) * 64 + 32);
+                sa[i] = __ldg(sc + (it0 + i) * 2);
+                sb[i] = __ldg(sc + (it0 + i) * 2 + 1);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const f2 a2 = bc2(sa[i]), b2 = bc2(sb[i]);
+                const f2 a0 = mul2(pair[wa[i] & 0xffu], a2), a1 = mul2(pair[wa[i] >> 8], a2);
+                const f2 b0 = mul2(pair[wb[i] & 0xffu], b2), b1 = mul2(pair[wb[i] >> 8], b2);
+                dst[(it0 + i) * 64] = make_float4(a0.x, a0.y, a1.x, a1.y);
+                dst[(it0 + i) * 64 + 32] = make_float4(b0.x, b0.y, b1.x, b1.y);
             }
         }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int64_t e = start + static_cast<int64_t>(it0 + i) * kPanelCols + lane * 8;
+        return;
+    }
+    for (int it = 0; it < kRowsPerItem; ++it) {
+        const int64_t e = start + static_cast<int64_t>(it) * kPanelCols + lane * 8;
         if (e >= numel) break;
         const int nv = static_cast<int>(min(static_cast<int64_t>(8), numel - e));
-        const uint32_t w = wv[i];
-        const float sc = scv[i];
+        const uint32_t w = load_codes(codes, e, nv, vec);
+        const float sc = __ldg(scales + (e >> 7));
         float v[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) v[k] = __fmul_rn(q[nib(w, k)], sc);
         store8_masked<float>(reinterpret_cast<char*>(out), e, nv, vec, v);
     }
+}
+
+// Rank-1 dequantize for matrices whose column count is a multiple of 256 (buffers vector-aligned), with the same
+// division of a row's 256-column panel among the lanes: 512 contiguous bytes per store instruction.  A lane keeps
+// the maxima of its 8 columns in registers; the next row's codes are requested before this row is worked on.
+__global__ void __launch_bounds__(kThreads)
+rank1_dequant_panel_kernel(const uint8_t* __restrict__ codes, const float* __restrict__ row_max, const float* __restrict__ col_max,
+                           int rows, int cols, float* __restrict__ out) {
+    __shared__ float2 pair[256];
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) pair[i] = make_float2(c_qv[i & 15], c_qv[i >> 4]);
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int panels = cols / kPanelCols;
+    const int64_t total = static_cast<int64_t>((rows + kRowsPerItem - 1) / kRowsPerItem) * panels;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * kWarpsPerCta;
+    for (int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5); item < total; item += stride) {
+        const int band = static_cast<int>(item / panels);
+        const int c0 = static_cast<int>(item - static_cast<int64_t>(band) * panels) * kPanelCols;   // first column of the panel
+        const int r0 = band * kRowsPerItem, r1 = min(r0 + kRowsPerItem, rows);
+        const float4 ca = __ldg(reinterpret_cast<const float4*>(col_max + c0) + lane);
+        const float4 cb = __ldg(reinterpret_cast<const float4*>(col_max + c0 + 128) + lane);
+        const uint16_t* c16 = reinterpret_cast<const uint16_t*>(codes) + lane;
+        int64_t e = static_cast<int64_t>(r0) * cols + c0;      // first element of the panel's row
+        uint32_t wa = __ldg(c16 + (e >> 2)), wb = __ldg(c16 + (e >> 2) + 32);
+        float row = __ldg(row_max + r0);
+        for (int r = r0; r < r1; ++r, e += cols) {
+            const uint32_t xa = wa, xb = wb;
+            const float rw = row;
+            if (r + 1 < r1) {
+                wa = __ldg(c16 + ((e + cols) >> 2));
+                wb = __ldg(c16 + ((e + cols) >> 2) + 32);
+                row = __ldg(row_max + r + 1);
+            }
+            const f2 a0 = mul2(pair[xa & 0xffu], mk2(fminf(rw, ca.x), fminf(rw, ca.y)));
+            const f2 a1 = mul2(pair[xa >> 8], mk2(fminf(rw, ca.z), fminf(rw, ca.w)));
+            const f2 b0 = mul2(pair[xb & 0xffu], mk2(fminf(rw, cb.x), fminf(rw, cb.y)));
+            const f2 b1 = mul2(pair[xb >> 8], mk2(fminf(rw, cb.z), fminf(rw, cb.w)));
+            float4* dst = reinterpret_cast<float4*>(out + e) + lane;
+            dst[0] = make_float4(a0.x, a0.y, a1.x, a1.y);
+            dst[32] = make_float4(b0.x, b0.y, b1.x, b1.y);
+        }
     }
 }
 
@@ -1254,7 +1333,9 @@ rank1_max_kernel(const float* __restrict__ v, int rows, int cols, float* __restr
         const int r0 = band * kPreRowsPerItem;  // tall items: one column atomic per 64 rows
         if (r0 >= rows) return;
         const int r1 = min(r0 + kPreRowsPerItem, rows);
-        const int j0 = static_cast<int>(item - static_cast<int64_t>(band) * panels) * kPanelCols + lane * 8;
+        // lane L takes columns 4L .. 4L+3 and 128+4L .. 128+4L+3 of the panel: each of its two 128-bit loads is one of
+        // 32 consecutive 16-byte pieces, a load instruction of the warp reads 512 contiguous bytes
+        const int c0 = static_cast<int>(item - static_cast<int64_t>(band) * panels) * kPanelCols;
         uint32_t cmax[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) cmax[k] = 0;
@@ -1263,7 +1344,12 @@ rank1_max_kernel(const float* __restrict__ v, int rows, int cols, float* __restr
         for (int rb = r0; rb < r1; rb += 4) {
             float x[4][8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) load8f(v, static_cast<int64_t>(min(rb + i, r1 - 1)) * cols + j0, x[i]);
+            for (int i = 0; i < 4; ++i) {
+                const float4* src = reinterpret_cast<const float4*>(v + static_cast<int64_t>(min(rb + i, r1 - 1)) * cols + c0) + lane;
+                const float4 a = __ldg(src), b = __ldg(src + 32);
+                x[i][0] = a.x; x[i][1] = a.y; x[i][2] = a.z; x[i][3] = a.w;
+                x[i][4] = b.x; x[i][5] = b.y; x[i][6] = b.z; x[i][7] = b.w;
+            }
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 uint32_t rmax = 0;
@@ -1278,7 +1364,7 @@ rank1_max_kernel(const float* __restrict__ v, int rows, int cols, float* __restr
             }
         }
 #pragma unroll
-        for (int k = 0; k < 8; ++k) atomic_max_nonneg(col_max + j0 + k, cmax[k]);
+        for (int k = 0; k < 8; ++k) atomic_max_nonneg(col_max + c0 + (k < 4 ? 0 : 124) + lane * 4 + k, cmax[k]);
     } else {
         const int64_t numel = static_cast<int64_t>(rows) * cols;
         const int64_t start = item * (kPanelCols * kRowsPerItem);
@@ -1301,13 +1387,12 @@ rank1_max_kernel(const float* __restrict__ v, int rows, int cols, float* __restr
     }
 }
 
-// The same for matrices whose column count is a multiple of 256 and whose buffers are vector-aligned: panel mapping
-// (a lane keeps its 8 column maxima in registers, the row maximum is one broadcast load per row), packed division
-// and the closed-form search where the scales allow it.
-template <bool QUANT>
+// Rank-1 quantize for matrices whose column count is a multiple of 256 and whose buffers are vector-aligned: panel
+// mapping (a lane keeps its 8 column maxima in registers, the row maximum is one broadcast load per row), packed
+// division and the closed-form search where the scales allow it.
 __global__ void __launch_bounds__(kThreads)
-rank1_codec_panel_kernel(const float* __restrict__ in, uint8_t* __restrict__ codes, const float* __restrict__ row_max,
-                         const float* __restrict__ col_max, int rows, int cols, float* __restrict__ out) {
+rank1_quant_panel_kernel(const float* __restrict__ in, uint8_t* __restrict__ codes, const float* __restrict__ row_max,
+                         const float* __restrict__ col_max, int rows, int cols) {
     __shared__ SmemPre s;
     load_smem(s);
     const int lane = threadIdx.x & 31;
@@ -1316,61 +1401,47 @@ rank1_codec_panel_kernel(const float* __restrict__ in, uint8_t* __restrict__ cod
     const int64_t stride = static_cast<int64_t>(gridDim.x) * kWarpsPerCta;
     for (int64_t item = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5); item < total; item += stride) {
         const int band = static_cast<int>(item / panels);
-        const int j0 = static_cast<int>(item - static_cast<int64_t>(band) * panels) * kPanelCols + lane * 8;
+        // lane L takes columns 4L .. 4L+3 and 128+4L .. 128+4L+3 of the panel (512 contiguous bytes per load instruction)
+        const int c0 = static_cast<int>(item - static_cast<int64_t>(band) * panels) * kPanelCols;
         const int r0 = band * kRowsPerItem, r1 = min(r0 + kRowsPerItem, rows);
         float col[8];
-        load8f(col_max, j0, col);
+        {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(col_max + c0) + lane), b = __ldg(reinterpret_cast<const float4*>(col_max + c0 + 128) + lane);
+            col[0] = a.x; col[1] = a.y; col[2] = a.z; col[3] = a.w;
+            col[4] = b.x; col[5] = b.y; col[6] = b.z; col[7] = b.w;
+        }
         bool ok = true;
 #pragma unroll
         for (int k = 0; k < 8; ++k) ok &= scale_safe(col[k]) && col[k] > 0.0f;
         const bool col_fast = __all_sync(kFull, ok);
         // the next row's input is requested before this row is worked on: two rows per warp in flight
-        float xn[8];
-        uint32_t wn = 0;
+        int64_t e = static_cast<int64_t>(r0) * cols + c0;
+        float4 na = __ldg(reinterpret_cast<const float4*>(in + e) + lane), nb = __ldg(reinterpret_cast<const float4*>(in + e) + lane + 32);
         float rown = __ldg(row_max + r0);
-        if (QUANT)
-            load8f(in, static_cast<int64_t>(r0) * cols + j0, xn);
-        else
-            wn = __ldg(reinterpret_cast<const uint32_t*>(codes + ((static_cast<int64_t>(r0) * cols + j0) >> 1)));
-        for (int r = r0; r < r1; ++r) {
-            const int64_t e = static_cast<int64_t>(r) * cols + j0;
+        for (int r = r0; r < r1; ++r, e += cols) {
             const float row = rown;
-            float x[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) x[k] = xn[k];
-            const uint32_t wcur = wn;
+            const float x[8] = {na.x, na.y, na.z, na.w, nb.x, nb.y, nb.z, nb.w};
             if (r + 1 < r1) {
                 rown = __ldg(row_max + r + 1);
-                if (QUANT)
-                    load8f(in, e + cols, xn);
-                else
-                    wn = __ldg(reinterpret_cast<const uint32_t*>(codes + ((e + cols) >> 1)));
+                na = __ldg(reinterpret_cast<const float4*>(in + e + cols) + lane);
+                nb = __ldg(reinterpret_cast<const float4*>(in + e + cols) + lane + 32);
             }
-            if (QUANT) {
-                uint32_t w = 0;
-                if (col_fast && scale_safe(row) && row > 0.0f) {  // warp-uniform
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const f2 sc = mk2(fminf(row, col[2 * j]), fminf(row, col[2 * j + 1]));
-                        const f2 y = fma2(div2(mk2(x[2 * j], x[2 * j + 1]), sc), bc2(16.0f), bc2(-1.5f));
-                        w += code_from_y(y.x) << (8 * j);
-                        w += code_from_y(y.y) << (8 * j + 4);
-                    }
-                } else {
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) w |= search16(scaled(x[k], fminf(row, col[k])), s.t.mv) << (4 * k);
-                }
-                *reinterpret_cast<uint32_t*>(codes + (e >> 1)) = w;
-            } else {
-                const uint32_t w = wcur;
+            uint32_t w = 0;   // codes of the first quad in bits 0..15, of the second in bits 16..31
+            if (col_fast && scale_safe(row) && row > 0.0f) {  // warp-uniform
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const f2 v = mul2(pair_lookup(s.qv2, w, j), mk2(fminf(row, col[2 * j]), fminf(row, col[2 * j + 1])));
-                    x[2 * j] = v.x;
-                    x[2 * j + 1] = v.y;
+                    const f2 sc = mk2(fminf(row, col[2 * j]), fminf(row, col[2 * j + 1]));
+                    const f2 y = fma2(div2(mk2(x[2 * j], x[2 * j + 1]), sc), bc2(16.0f), bc2(-1.5f));
+                    w += code_from_y(y.x) << (8 * j);
+                    w += code_from_y(y.y) << (8 * j + 4);
                 }
-                Elem<float>::store8(reinterpret_cast<char*>(out), e, x);
+            } else {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) w |= search16(scaled(x[k], fminf(row, col[k])), s.t.mv) << (4 * k);
             }
+            uint16_t* c16 = reinterpret_cast<uint16_t*>(codes) + (e >> 2) + lane;
+            c16[0] = static_cast<uint16_t>(w);
+            c16[32] = static_cast<uint16_t>(w >> 16);
         }
     }
 }

@@ -85,17 +85,18 @@ __device__ __forceinline__ f2 div2_prepared(f2 a, f2 r, f2 nd) {
 }
 
 // The same with one residual correction.  With q0 = RN(a r) and the exact residual t = a - d q0, the value
-// q0 + t r differs from a / d by |a / d - q0| * |1 - d r|, below 2^-45 |a / d| for a reciprocal within two units in
-// the last place; its rounding is therefore the correctly rounded quotient unless a / d lies within that distance of
-// the midpoint of two neighbouring floats.  Quotients of two 24-bit operands come no closer to such a midpoint than
-// about 2^-49 relative, so the exceptions exist but are rare: about one operand pair in 10^7 gets the neighbouring
-// float (tests/cuda/math_check.cu measures the rate).  The step uses this form where the deviation cannot be seen
-// in a result except through a second coincidence:
+// q0 + t r differs from a / d by |a / d - q0| * |1 - d r|: a few 2^-47 |a / d| for a reciprocal within a unit in the
+// last place.  Its rounding is therefore the correctly rounded quotient unless a / d lies within that distance of the
+// midpoint of two neighbouring floats.  Quotients of two 24-bit operands can come that close to such a midpoint (the
+// closest is about 2^-49 relative), so exceptions exist, but they are rare and never more than one unit in the last
+// place: 0 (reciprocal from rcp.rn) and 1 (reciprocal from the approximation unit) of 1.2 * 10^9 random operand pairs
+// in tests/cuda/math_check.cu, which re-measures the rate on every run.  The step uses this form where such a
+// deviation cannot reach a result except through a second coincidence:
 //   * requantization: the quotient only selects a code, which changes only if the two candidate quotients also
-//     straddle one of the 15 code boundaries (together about 10^-13 per element; a differing code is then one level
-//     off at an exact near-tie, the case for which the contract allows a fraction of 10^-6);
-//   * the update of bf16 parameters: the quotient enters a sum that is rounded to 8 bits of mantissa (about 10^-13
-//     per element again).  fp32 parameters keep the second correction: there the last place of the quotient is visible.
+//     straddle one of the 15 code boundaries (of the order of 10^-15 per element; a differing code would then be one
+//     level off at an exact near-tie, the case for which the contract allows a fraction of 10^-6);
+//   * the update of bf16 parameters: the quotient enters a sum that is then rounded to 8 bits of mantissa.
+// fp32 parameters keep the second correction: there the last place of the quotient is visible in the result.
 __device__ __forceinline__ f2 div2_prepared1(f2 a, f2 r, f2 nd) {
     const f2 q = mul2(a, r);
     const f2 t = fma2(nd, q, a);

@@ -317,10 +317,20 @@ class FourBitAdamW(torch.optim.Optimizer):
         for p, _, st, hi in entries:
             if classes[hi] is None:
                 classes[hi] = [group_of[id(p)], float(st["step"]), st["step"]]
+        # All step counters of the launch become views of one vector, so that the steady state advances them with a
+        # single in-place add instead of one per parameter (a state dict still sees a 0-dim float32 tensor each).
+        steps_vec = torch.stack([st["step"].reshape(()) for _, _, st, _ in entries])
+        for i, (_, _, st, _) in enumerate(entries):
+            st["step"] = steps_vec[i]
+        for c in classes:
+            c[2] = None
+        for (_, _, st, hi) in entries:
+            if classes[hi][2] is None:
+                classes[hi][2] = st["step"]
         self._fast = {
             "dev": dev, "plan": self._plans[(dev.index, 0)], "checks": [(p, p.data_ptr(), g.data_ptr()) for p, g, _, _ in entries],
             "absent": [p for g in self.param_groups for p in g["params"] if id(p) not in seen],
-            "steps": [st["step"] for _, _, st, _ in entries], "classes": classes,
+            "steps_vec": steps_vec, "classes": classes,
             "n_params": sum(len(g["params"]) for g in self.param_groups),
         }
 
@@ -351,7 +361,7 @@ class FourBitAdamW(torch.optim.Optimizer):
             checks[i] = (checks[i][0], checks[i][1], g.data_ptr())
         if moved:
             plan.signature = None     # the slow path must not trust its cached signature any more
-        torch._foreach_add_(f["steps"], 1.0)
+        f["steps_vec"].add_(1.0)
         hypers = []
         for c in f["classes"]:
             c[1] += 1.0
