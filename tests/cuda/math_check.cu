@@ -171,6 +171,68 @@ __global__ void k_dequant_v(uint32_t lo, uint64_t count, Report* r) {
     }
 }
 
+// ---- dispatch probe ------------------------------------------------------------------------------------------
+// How many cycles an SM sub-partition needs per warp instruction of a class, alone and mixed 1 : 1 with packed FMAs:
+// NF independent packed FMAs and NA independent instructions of class KIND (0 lop3, 1 prmt, 2 funnel shift, 3 integer
+// multiply-add, 4 scalar fma) per group, four warps per sub-partition.  The design notes quote these figures for the
+// statement that the step kernels are bound by instruction dispatch.
+template <int NF, int NA, int KIND>
+__global__ void __launch_bounds__(256) k_probe(float2* out, unsigned* iout, int iters, float2 a, float2 b, unsigned k) {
+    float2 f[8];
+    unsigned u[8];
+    float s[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        f[i] = make_float2(threadIdx.x + i, i);
+        u[i] = threadIdx.x * 7 + i;
+        s[i] = i + threadIdx.x;
+    }
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int rep = 0; rep < 4; ++rep) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (i < NF) f[i] = __ffma2_rn(f[i], a, b);
+                if (i < NA) {
+                    unsigned& x = u[i];
+                    if (KIND == 0) asm volatile("lop3.b32 %0, %1, %2, %3, 0x6a;" : "=r"(x) : "r"(x), "r"(k), "r"(u[(i + 3) & 7]));
+                    if (KIND == 1) asm volatile("prmt.b32 %0, %1, %2, 0x3021;" : "=r"(x) : "r"(x), "r"(k));
+                    if (KIND == 2) x = __funnelshift_r(x, k, 3);
+                    if (KIND == 3) asm volatile("mad.lo.u32 %0, %1, %2, %3;" : "=r"(x) : "r"(x), "r"(k), "r"(u[(i + 3) & 7]));
+                    if (KIND == 4) s[i] = __fmaf_rn(s[i], a.x, b.x);
+                }
+            }
+        }
+    }
+    float2 acc = make_float2(0, 0);
+    unsigned ua = 0;
+    for (int i = 0; i < 8; ++i) {
+        acc.x += f[i].x + s[i];
+        acc.y += f[i].y;
+        ua += u[i];
+    }
+    out[blockIdx.x * blockDim.x + threadIdx.x] = acc;
+    iout[blockIdx.x * blockDim.x + threadIdx.x] = ua;
+}
+
+template <int NF, int NA, int KIND>
+double probe_ms(float2* out, unsigned* iout, int iters) {
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    const float2 a = make_float2(1.0001f, 0.9f), b = make_float2(0.5f, 0.25f);
+    k_probe<NF, NA, KIND><<<148 * 2, 256>>>(out, iout, 50, a, b, 0x1234u);
+    cudaEventRecord(e0);
+    k_probe<NF, NA, KIND><<<148 * 2, 256>>>(out, iout, iters, a, b, 0x1234u);
+    cudaEventRecord(e1);
+    cudaDeviceSynchronize();
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    return ms;
+}
+
 int finish(Report* d, unsigned long long* checked_bad, unsigned int* first) {
     Report h;
     cudaError_t e = cudaDeviceSynchronize();
@@ -260,6 +322,32 @@ int qfc_dequant_v(uint32_t lo_bits, uint64_t count, unsigned long long* bad, uns
     if (!d) return 1;
     k_dequant_v<<<148 * 8, 256>>>(lo_bits, count, d);
     return finish(d, bad, first);
+}
+
+// out[0..10]: milliseconds of (packed FMA alone; lop3, prmt, shift, imad, scalar fma alone; each of those five mixed
+// 1 : 1 with packed FMAs), 8 instructions of each class per group; out[11] = groups per warp.  Four warps per SM
+// sub-partition, so cycles per group per sub-partition = ms * clock / (4 * groups).
+int qfc_issue_probe(double* out) {
+    float2* o = nullptr;
+    unsigned* io = nullptr;
+    if (cudaMalloc(&o, 148 * 2 * 256 * sizeof(float2)) != cudaSuccess || cudaMalloc(&io, 148 * 2 * 256 * 4) != cudaSuccess) return 1;
+    const int iters = 5000;
+    out[0] = probe_ms<8, 0, 0>(o, io, iters);
+    out[1] = probe_ms<0, 8, 0>(o, io, iters);
+    out[2] = probe_ms<0, 8, 1>(o, io, iters);
+    out[3] = probe_ms<0, 8, 2>(o, io, iters);
+    out[4] = probe_ms<0, 8, 3>(o, io, iters);
+    out[5] = probe_ms<0, 8, 4>(o, io, iters);
+    out[6] = probe_ms<8, 8, 0>(o, io, iters);
+    out[7] = probe_ms<8, 8, 1>(o, io, iters);
+    out[8] = probe_ms<8, 8, 2>(o, io, iters);
+    out[9] = probe_ms<8, 8, 3>(o, io, iters);
+    out[10] = probe_ms<8, 8, 4>(o, io, iters);
+    out[11] = 4.0 * iters;
+    const cudaError_t e = cudaDeviceSynchronize();
+    cudaFree(o);
+    cudaFree(io);
+    return e == cudaSuccess ? 0 : 1;
 }
 
 int qfc_threads(void) { return 148 * 8 * 256; }

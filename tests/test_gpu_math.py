@@ -100,3 +100,28 @@ def test_mantissa_trick_dequantize_matches_table_times_scale(mc):
     assert bad == 0, first
     bad, first = _call(mc.qfc_dequant_v, C.c_uint32(0x2f000000), C.c_uint64(1 << 28))   # around 1e-10 .. 1e-1
     assert bad == 0, first
+
+
+def test_dispatch_probe_packed_and_integer_instructions_do_not_overlap_for_free(mc):
+    """Cycles per warp instruction on one SM sub-partition (four warps), alone and mixed 1 : 1 with packed FMAs: the
+    yardstick behind the statement that the step kernels are bound by instruction dispatch.  Printed for the record;
+    asserted loosely (a scalar FMA dispatches in about one cycle, a packed one in about two, and an integer
+    instruction mixed in costs about a cycle more, never nothing)."""
+    import torch
+    out = (C.c_double * 12)()
+    assert mc.qfc_issue_probe(out) == 0
+    try:
+        mhz = float(torch.cuda.get_device_properties(0).clock_rate) / 1e3    # maximum SM clock; the probe runs at it
+    except Exception:  # noqa: BLE001
+        mhz = 1965.0
+    per_group = [out[i] * 1e-3 * mhz * 1e6 / (4 * out[11]) for i in range(11)]     # cycles per group of 8 (+8) instructions
+    names = ["packed fma", "lop3", "prmt", "funnel shift", "imad", "scalar fma"]
+    alone = {n: per_group[i] / 8 for i, n in enumerate(names)}
+    mixed = {n: per_group[6 + i] / 8 for i, n in enumerate(names[1:])}
+    print(f"SM clock assumed {mhz} MHz; cycles per instruction alone: " + ", ".join(f"{n} {v:.2f}" for n, v in alone.items()))
+    print("cycles per (packed fma + one instruction of the class): " + ", ".join(f"{n} {v:.2f}" for n, v in mixed.items()))
+    assert 0.8 < alone["scalar fma"] < 1.4
+    assert 1.7 < alone["packed fma"] < 2.8
+    for n in ("lop3", "prmt", "funnel shift"):
+        assert mixed[n] > alone["packed fma"] + 0.5, n          # not hidden behind the packed FMAs
+    assert mixed["imad"] > alone["packed fma"] + 1.5             # shares the FMA pipe: fully additive
