@@ -436,8 +436,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=[None, *S.WORKLOADS, "quantize"])
-    ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "p2p"],
-                    help="N>1: how the updated parameters reach the other ranks (peer stores from the update kernel, or an all-gather)")
+    ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "p2p", "ce"],
+                    help="N>1: how the updated parameters reach the other ranks (copy engines piece by piece, peer stores from "
+                         "the update kernel, or an all-gather afterwards)")
     ap.add_argument("--start-step", type=int, default=0,
                     help="N=1: set every step counter to this value after the warm-up (>= 20000 shows the late-training "
                          "regime where sqrt(1 - beta2^t) has rounded to 1)")

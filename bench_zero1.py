@@ -1,8 +1,9 @@
 """Multi-GPU leg of bench.py: the optimizer state sharded over the ranks (ShardedFourBitAdamW), one process per GPU
 under torchrun.  The headline workload is the same at every N -- the Llama-7B-shaped set, so the lines at N = 1, 2, 4, 8
 form one strong-scaling curve -- and the Llama-13B-shaped set is reported beside it.  NCCL carries the max exchange; the
-updated bf16 parameters reach the other ranks through peer stores issued by the update kernel itself (comm "p2p", the
-default where it can be set up) or through an NCCL all-gather after it (comm "nccl").
+updated bf16 parameters reach the other ranks while the update computes -- through peer stores issued by the update kernel
+itself (comm "p2p", the default where it can be set up) or in pieces through the copy engines (comm "ce") -- or through an
+NCCL all-gather after it (comm "nccl").
 
 Every measured workload ends with two checks: the flat parameter buffers of all ranks must be identical (a 64-bit
 checksum, minimum and maximum over the ranks), and one whole tensor -- one that is cut between ranks where there is
@@ -145,7 +146,7 @@ def measure(bench, workload: str, hp, args, dev, rank: int, world: int, detail: 
             reduce_ms += e[0].elapsed_time(e[1]) / reps
         reduce_ms = _max_over_ranks(reduce_ms, dev)
     push_ms = None
-    if opt.comm == "p2p":   # the fused main pass: update + peer stores, closed by the small collective
+    if opt.comm in ("p2p", "ce"):   # the main pass with the delivery inside it (peer stores, or pieces + copy engines), closed by the small collective
         push_ms = 0.0
         for _ in range(reps):
             opt.step_pre()
@@ -153,7 +154,10 @@ def measure(bench, workload: str, hp, args, dev, rank: int, world: int, detail: 
                 dist.all_reduce(opt.shared_new, op=dist.ReduceOp.MAX)
             dist.barrier()
             e[0].record()
-            opt.backend.main_push(opt.states, opt._hyper, opt.peer_deltas)
+            if opt.comm == "p2p":
+                opt.backend.main_push(opt.states, opt._hyper, opt.peer_deltas)
+            else:
+                opt._main_ce()
             dist.all_reduce(opt._token, op=dist.ReduceOp.MAX)
             e[1].record()
             torch.cuda.synchronize(dev)
@@ -245,7 +249,7 @@ def run(args, hp) -> None:
             "params": a["params"], "ms_per_step": a["ms_per_step"], "Gparams_per_s": a["params"] / (a["ms_per_step"] * 1e-3) / 1e9,
             "comm": a["comm"], "shard_step_ms": a["parts"][0] + a["parts"][1],
             "parts_ms": {"pre+max_exchange": a["parts"][0], "main": a["parts"][1], "all_gather": a["parts"][2],
-                         "main_with_peer_stores": a["push_ms"]},
+                         "main_with_delivery": a["push_ms"]},
             "delivery_bytes_per_gpu": gather, "delivery_bound_ms": gather / (link["all_to_all"] * 1e9) * 1e3,
             "replicas_identical": a["replicas_identical"], "oracle_subset": a["oracle_subset"]}}
 
@@ -280,7 +284,8 @@ def run(args, hp) -> None:
                                       "grad_reduce_scatter": m["reduce_ms"]},
                          "all_gather": {"bytes_received_per_gpu": gather_bytes,
                                         "GBps_per_gpu": gather_bytes / (parts[2] * 1e-3) / 1e9 if parts[2] else None},
-                         "main_with_peer_stores": None if push_ms is None else {
+                         "main_with_delivery": None if push_ms is None else {
+                             "how": "peer stores from the update kernel" if m["comm"] == "p2p" else "update in pieces, copy engines deliver each finished piece",
                              "ms": push_ms, "bytes_sent_per_gpu": gather_bytes,
                              "GBps_per_gpu": gather_bytes / (push_ms * 1e-3) / 1e9,
                              "frac_of_measured_copy_rate": gather_bytes / (push_ms * 1e-3) / 1e9 / rate,

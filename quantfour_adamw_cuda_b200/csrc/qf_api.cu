@@ -511,6 +511,18 @@ int qf_peer_close(void* base, int device) {
     return fail(QF_ERR_BAD_ARG, "qf_peer_close: %p is not a mapping qf_peer_open returned", base);
 }
 
+int qf_peer_copy(void* dst, int dst_device, const void* src, size_t bytes, int device, void* stream) {
+    g_err[0] = 0;
+    if (bytes == 0) return QF_OK;
+    if (!dst || !src) return fail(QF_ERR_BAD_ARG, "qf_peer_copy: null pointer");
+    QF_CUDA(cudaSetDevice(device));
+    if (dst_device >= 0)   // the explicit peer form: takes the direct device-to-device path also for mappings of another process's memory
+        QF_CUDA(cudaMemcpyPeerAsync(dst, dst_device, src, device, bytes, static_cast<cudaStream_t>(stream)));
+    else
+        QF_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)));
+    return QF_OK;
+}
+
 int qf_read_status(void* workspace, int device, void* stream, uint32_t* status) {
     g_err[0] = 0;
     if (!workspace || !status) return fail(QF_ERR_BAD_ARG, "null workspace or status pointer");

@@ -8,10 +8,13 @@ multiple of 128 elements so that its 128-element quantization blocks coincide wi
 space.  The flat space is cut into `world` equal ranges of `shard` elements (a multiple of 128).  Rank r
 owns the optimizer state of range r and updates the parameters in it; parameters and gradients stay
 replicated.  After the step each rank's range is all-gathered in place into every rank's flat buffer
-(`comm="nccl"`), or -- when the ranks are processes of one node whose devices reach one another's memory
-(`comm="p2p"`, what `comm="auto"` picks if the set-up succeeds on every rank) -- the update kernel itself stores
-each new parameter vector into every peer's flat buffer over NVLink while it computes, and no all-gather
-follows (qf_step_main_push).
+(`comm="nccl"`), or -- when the ranks are processes of one node whose devices reach one another's memory -- the
+new parameters cross NVLink while the update still computes and no all-gather follows: the update kernel itself
+stores each new parameter vector into every peer's flat buffer (`comm="p2p"`, qf_step_main_push; what `comm="auto"`
+picks if the set-up succeeds on every rank), or the rank updates its range in pieces and the copy engines carry each
+finished piece to every peer on side streams (`comm="ce"`: the copy engines alone move 10 % more bytes per second than
+stores issued by a kernel, but copies in flight slow the update kernels beside them several times over on this
+hardware, so this form measured slower and is kept as an option only).
 
 A 2-D tensor cut by a range boundary keeps its rank-1 second-moment scales identical to the unsharded
 optimizer: the new row / column maxima of such a tensor are combined with an element-wise max over the
@@ -333,8 +336,8 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
             raise TypeError(f"parameters must be float32 or bfloat16, got {p0.dtype}")
         self.layout = flat_layout([p.shape for p in self.params], self.world)
         self.step_count = 0
-        if comm not in ("auto", "nccl", "p2p"):
-            raise ValueError(f"comm must be 'auto', 'nccl' or 'p2p', got {comm!r}")
+        if comm not in ("auto", "nccl", "p2p", "ce"):
+            raise ValueError(f"comm must be 'auto', 'nccl', 'p2p' or 'ce', got {comm!r}")
         self._flatten()
         self._build_state()
         self.reduce_grads = bool(reduce_grads)
@@ -343,10 +346,11 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
             self.flat_grad = torch.zeros_like(self.flat)
             self._attach_grad_views()
         self.peer_deltas: List[int] = []
+        self.peer_devices: List[int] = []
         self._peer_bases: List[int] = []
         self.comm = self._comm_selected = "nccl"
         if comm != "nccl" and self.sharded and self.world > 1 and self.flat.is_cuda:
-            self._setup_p2p(required=comm == "p2p")
+            self._setup_p2p(required=comm in ("p2p", "ce"), mode="ce" if comm == "ce" else "p2p")
 
     # ---- set-up -----------------------------------------------------------------------------------
 
@@ -443,7 +447,7 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
                     st.v_col, st.col_new, st.col_rcp = old[Rp:Rp + Cc], new[Rp:Rp + Cc], rcp[Rp:Rp + Cc]
             self.states.append(st)
 
-    def _setup_p2p(self, required: bool) -> None:
+    def _setup_p2p(self, required: bool, mode: str = "p2p") -> None:
         """Map every other rank's flat buffer into this process.  All ranks take the same decision: one
         failure anywhere (devices of different nodes, no peer access, a virtual-memory allocator) keeps the
         all-gather."""
@@ -451,7 +455,7 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
         self._token = torch.zeros(1, dtype=torch.float32, device=dev)
         err, mine = "", None
         try:
-            mine = self.backend.export_buffer(self.flat) + (socket.gethostname(),)
+            mine = self.backend.export_buffer(self.flat) + (socket.gethostname(), str(torch.cuda.get_device_properties(dev).uuid))
         except Exception as e:  # noqa: BLE001 - any failure means: no peer path
             err = f"{type(e).__name__}: {e}"
         everyone: List[Any] = [None] * self.world
@@ -460,12 +464,16 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
             err = "the ranks run on different hosts"     # a handle means nothing on another machine: do not try it
         if not err and all(x is not None for x in everyone) and self.world - 1 <= _lib.QF_MAX_PEERS:
             try:
-                for r, (handle, off, _) in enumerate(everyone):
-                    if r == self.rank:
-                        continue
+                visible = {str(torch.cuda.get_device_properties(i).uuid): i for i in range(torch.cuda.device_count())}
+                # peers in rotated order (rank + 1, rank + 2, ...): whatever walks the list -- the stores of a row, the
+                # copies of a piece -- then targets a different GPU on every rank at any moment
+                for k in range(1, self.world):
+                    r = (self.rank + k) % self.world
+                    handle, off, _, uuid = everyone[r]
                     base, addr = self.backend.open_buffer(handle, off, dev)
                     self._peer_bases.append(base)
                     self.peer_deltas.append(addr - self.flat.data_ptr())
+                    self.peer_devices.append(visible.get(uuid, -1))   # the peer's GPU as this process numbers it
             except Exception as e:  # noqa: BLE001
                 err = f"{type(e).__name__}: {e}"
         elif not err:
@@ -473,11 +481,53 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
         ok = torch.tensor([0.0 if err else 1.0], device=dev)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
         if ok.item() == 1.0:
-            self.comm = self._comm_selected = "p2p"
+            self.comm = self._comm_selected = mode
+            if mode == "ce":
+                self._setup_chunks()
             return
         self.close()
         if required:
             raise RuntimeError(f"comm='p2p' is not available on rank {self.rank}: {err or 'another rank failed'}")
+
+    def _setup_chunks(self, max_chunks: int = 8, min_bytes: int = 64 << 20) -> None:
+        """Cut this rank's records into consecutive pieces of about equal size (all records of one tensor stay together:
+        they share its row / column buffers) for the pipelined delivery: one update call and one copy per peer each."""
+        esz = self.flat.element_size()
+        total = sum(st.rec.numel for st in self.states)
+        k = max(1, min(max_chunks, total * esz // min_bytes))
+        target = -(-total // k)
+        self.chunks: List[Tuple[List[RecordState], int, int]] = []
+        cur: List[RecordState] = []
+        acc = 0
+        for i, st in enumerate(self.states):
+            cur.append(st)
+            acc += st.rec.numel
+            last_of_tensor = i + 1 == len(self.states) or self.states[i + 1].rec.tensor != st.rec.tensor
+            if last_of_tensor and (acc >= target or i + 1 == len(self.states)):
+                lo = self.layout.offsets[cur[0].rec.tensor] + cur[0].rec.a
+                hi = self.layout.offsets[cur[-1].rec.tensor] + cur[-1].rec.b
+                self.chunks.append((cur, lo, hi))
+                cur, acc = [], 0
+        self._chunk_backends = [CudaBackend() for _ in self.chunks]
+        dev = self.flat.device
+        self._ce_streams = [torch.cuda.Stream(dev) for _ in self.peer_deltas]
+        self._ce_events = [torch.cuda.Event() for _ in self.chunks]
+
+    def _main_ce(self) -> None:
+        """Second half of a step, delivery included: update piece k, then let the copy engines carry it to every
+        peer on side streams while piece k + 1 is updated."""
+        dev = self.flat.device
+        cur = torch.cuda.current_stream(dev)
+        base, esz, L = self.flat.data_ptr(), self.flat.element_size(), _lib.lib()
+        for (states, lo, hi), backend, ev in zip(self.chunks, self._chunk_backends, self._ce_events):
+            backend.main(states, self._hyper)
+            ev.record(cur)
+            for delta, pdev, stream in zip(self.peer_deltas, self.peer_devices, self._ce_streams):
+                stream.wait_event(ev)
+                _lib.check(L.qf_peer_copy(C.c_void_p(base + delta + lo * esz), pdev, C.c_void_p(base + lo * esz), (hi - lo) * esz,
+                                          dev.index, C.c_void_p(stream.cuda_stream)), "qf_peer_copy")
+        for stream in self._ce_streams:     # the next use of the stream (and of the flat buffer) comes after the copies
+            cur.wait_stream(stream)
 
     def close(self) -> None:
         """Unmap the peers' buffers (the optimizer falls back to the all-gather afterwards)."""
@@ -486,7 +536,7 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
                 self.backend.close_buffer(base, self.flat.device)
             except Exception:  # noqa: BLE001 - shutting down
                 pass
-        self._peer_bases, self.peer_deltas, self.comm = [], [], "nccl"
+        self._peer_bases, self.peer_deltas, self.peer_devices, self.comm = [], [], [], "nccl"
 
     def __del__(self):
         try:    # peer mappings must not outlive the optimizer; explicit close() stays the orderly way
@@ -517,6 +567,13 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
         if multi and self.shared_new.numel():
             # element-wise max of the new row / column maxima of the tensors that are cut between ranks
             dist.all_reduce(self.shared_new, op=dist.ReduceOp.MAX, group=self.group)
+        if multi and self.comm == "ce":
+            if not self.shared_new.numel():
+                dist.all_reduce(self._token, op=dist.ReduceOp.MAX, group=self.group)
+            # same ordering argument as for the peer stores below: one collective on either side of the delivery
+            self._main_ce()
+            dist.all_reduce(self._token, op=dist.ReduceOp.MAX, group=self.group)
+            return loss
         if multi and self.comm == "p2p":
             if not self.shared_new.numel():
                 dist.all_reduce(self._token, op=dist.ReduceOp.MAX, group=self.group)
@@ -534,8 +591,11 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
     def nonfinite_seen(self) -> bool:
         """Synchronise and report whether any step of this rank since the last call produced a non-finite scale
         (a non-finite gradient, or an overflow): the same question FourBitAdamW.nonfinite_seen answers."""
-        read = getattr(self.backend, "read_status", None)
-        return bool(read() & _lib.QF_STATUS_NONFINITE) if read else False
+        word = 0
+        for b in [self.backend] + list(getattr(self, "_chunk_backends", [])):
+            read = getattr(b, "read_status", None)
+            word |= read() if read else 0
+        return bool(word & _lib.QF_STATUS_NONFINITE)
 
     @torch.no_grad()
     def step_pre(self) -> None:

@@ -1,6 +1,6 @@
 """One process per GPU on every GPU of the machine (2 to 8): the sharded step with the parameters delivered by peer
-stores from the update kernel (comm="p2p") must leave the same bits as the all-gather path (comm="nccl") and as the
-unsharded oracle, for bf16 and fp32 parameters, with a shape list whose largest matrix is cut by three or more ranks
+stores from the update kernel (comm="p2p") or by the copy engines piece by piece (comm="ce") must leave the same bits as
+the all-gather path (comm="nccl") and as the unsharded oracle, for bf16 and fp32 parameters, with a shape list whose largest matrix is cut by three or more ranks
 at 8 ranks; then the same with per-rank gradients and the reduce-scatter inside the step.  Skipped on a single-GPU
 machine."""
 import os
@@ -31,7 +31,7 @@ for dtype in (torch.bfloat16, torch.float32):
     want = [p.clone() for p in init]
     states = [TO.TensorState.zeros(s) for s in SHAPES]
     runs = {}
-    for comm in ("p2p", "nccl"):
+    for comm in ("p2p", "ce", "nccl"):
         params = [torch.nn.Parameter(p.to(dev)) for p in init]
         runs[comm] = (params, ShardedFourBitAdamW(params, lr=1e-3, comm=comm))
         assert runs[comm][1].comm == comm, (comm, runs[comm][1].comm)
@@ -47,11 +47,14 @@ for dtype in (torch.bfloat16, torch.float32):
     for comm, (params, opt) in runs.items():
         for i, (p, w) in enumerate(zip(params, want)):
             assert torch.equal(p.detach().cpu(), w), f"rank {rank} {comm} {dtype} tensor {i} {SHAPES[i]}"
-    assert torch.equal(runs["p2p"][1].flat, runs["nccl"][1].flat)
+    assert torch.equal(runs["p2p"][1].flat, runs["nccl"][1].flat) and torch.equal(runs["ce"][1].flat, runs["nccl"][1].flat)
+    if dtype == torch.bfloat16:
+        assert len(runs["ce"][1].chunks) >= 1
     lay = runs["p2p"][1].layout
     cut = max(len(lay.owners(t)) for t in range(len(SHAPES)))
     assert cut >= min(world, 3), f"the shape list should put one tensor on {min(world, 3)} or more ranks, got {cut}"
     runs["p2p"][1].close()
+    runs["ce"][1].close()
 # the ranks hold different gradients; the step starts with the reduce-scatter (mean) of the flat gradient buffer
 for dtype in (torch.bfloat16, torch.float32):
     gen = torch.Generator().manual_seed(9)
@@ -93,4 +96,4 @@ def test_peer_stores_match_all_gather_and_oracle_on_every_gpu(tmp_path):
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     for r in range(nproc):
         assert f"rank {r} ok" in out.stdout
-    print(f"{nproc} ranks: p2p == nccl == oracle (bf16, fp32), reduce_grads == oracle")
+    print(f"{nproc} ranks: p2p == ce == nccl == oracle (bf16, fp32), reduce_grads == oracle")
