@@ -168,12 +168,14 @@ int qf_peer_close(void* base, int device);
 /*
  * Copy `bytes` bytes from this device's memory to a buffer mapped with qf_peer_open, asynchronously on `stream`,
  * through the copy engines.  `dst_device` is the ordinal, in this process, of the device that holds `dst` (a negative
- * value lets the runtime work it out, which was measured at half the rate for mappings of another process's memory).  The other way to deliver a
- * sharded step's new parameters: the rank updates its range in pieces with qf_step_main and copies each finished
- * piece to every peer on side streams while the next piece computes.  On this hardware the copy engines move about
- * 770-800 GB/s per GPU with all GPUs sending to all others, stores issued by a kernel (qf_step_main_push) about 690;
- * but update kernels that run beside copies in flight were measured several times slower, so the pipelined form lost
- * to qf_step_main_push (23.4 against 15.8 ms per step on 4 GPUs, 7B shape).  No counterpart in the reference.
+ * value lets the runtime work it out).  The other way to deliver a sharded step's new parameters: the rank updates
+ * its range in pieces with qf_step_main and copies each finished piece to every peer on side streams while the next
+ * piece computes.  Measured on 4 and 8 B200s (7B shape): with every GPU copying to all others at once, peers taken in
+ * rotated order (rank+1, rank+2, ...), the copy engines move 770-800 GB/s per GPU, stores issued by a kernel
+ * (qf_step_main_push) about 690; but in the pipelined step the engines serve the per-peer streams one after another
+ * in an order the caller does not control, the ranks drift apart, several senders meet at one receiver, and the step
+ * took 22-23 ms against 15.8 ms with qf_step_main_push, whose every warp spreads its stores evenly over all peers.
+ * No counterpart in the reference.
  */
 int qf_peer_copy(void* dst, int dst_device, const void* src, size_t bytes, int device, void* stream);
 

@@ -13,8 +13,9 @@ new parameters cross NVLink while the update still computes and no all-gather fo
 stores each new parameter vector into every peer's flat buffer (`comm="p2p"`, qf_step_main_push; what `comm="auto"`
 picks if the set-up succeeds on every rank), or the rank updates its range in pieces and the copy engines carry each
 finished piece to every peer on side streams (`comm="ce"`: the copy engines alone move 10 % more bytes per second than
-stores issued by a kernel, but copies in flight slow the update kernels beside them several times over on this
-hardware, so this form measured slower and is kept as an option only).
+stores issued by a kernel, but the engines serve the per-peer streams in an order of their own, the ranks drift
+apart and several senders meet at one receiver, so this form measured slower -- 22-23 against 15.8 ms per step on
+4 GPUs, 7B shape -- and is kept as an option only).
 
 A 2-D tensor cut by a range boundary keeps its rank-1 second-moment scales identical to the unsharded
 optimizer: the new row / column maxima of such a tensor are combined with an element-wise max over the

@@ -97,6 +97,39 @@ def test_emulated_ranks_with_peer_stores(world, dtype):
             assert torch.equal(p.detach().cpu(), w), f"tensor {i} {SHAPES[i]} differs in {(p.detach().cpu() != w).sum()} places"
 
 
+@pytest.mark.parametrize("world", [2, 3])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_emulated_ranks_with_pipelined_copies(world, dtype):
+    """The update in pieces (one qf_step_main per piece) with qf_peer_copy carrying each finished piece into the
+    other ranks' flat buffers (same device here)."""
+    init, grads, want = _oracle_run(dtype, 4, 3)
+    ranks = []
+    for r in range(world):
+        params = [torch.nn.Parameter(p.cuda()) for p in init]
+        opt = ShardedFourBitAdamW(params, lr=1e-3, rank=r, world=world)
+        ranks.append((params, opt))
+    for _, opt in ranks:
+        opt.peer_deltas = [other.flat.data_ptr() - opt.flat.data_ptr() for _, other in ranks if other is not opt]
+        opt.peer_devices = [-1] * len(opt.peer_deltas)
+        opt._setup_chunks(max_chunks=3, min_bytes=1)
+    assert max(len(opt.chunks) for _, opt in ranks) > 1
+    for gs in grads:
+        for params, opt in ranks:
+            for p, g in zip(params, gs):
+                p.grad = g.cuda()
+            opt.step_pre()
+        if ranks[0][1].shared_new.numel():
+            combined = torch.stack([opt.shared_new for _, opt in ranks]).max(dim=0).values
+            for _, opt in ranks:
+                opt.shared_new.copy_(combined)
+        for _, opt in ranks:
+            opt._main_ce()
+    torch.cuda.synchronize()
+    for params, _ in ranks:
+        for i, (p, w) in enumerate(zip(params, want)):
+            assert torch.equal(p.detach().cpu(), w), f"tensor {i} {SHAPES[i]} differs in {(p.detach().cpu() != w).sum()} places"
+
+
 def test_push_rejects_bad_peers():
     params = [torch.nn.Parameter(torch.zeros(64, 256, device="cuda"))]
     opt = ShardedFourBitAdamW(params, lr=1e-3)
