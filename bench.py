@@ -269,21 +269,50 @@ def single_gpu(args):
         for p, g in zip(params, dst):
             p.grad = g
 
-        def e2e_step():
-            for hsrc, d in zip(host, dst):
-                d.copy_(hsrc, non_blocking=True)
-            opt.step()
-            return opt.nonfinite_seen()   # device -> host read of the step's status word; synchronises
+        # The way a host that holds the gradients would drive the public API: the parameter list in eight groups of about
+        # equal bytes, one optimizer each; the copies of all groups go out on a copy stream, and the step of group k
+        # starts when its gradients have arrived, while those of group k + 1 are still crossing PCIe.
+        n_groups = 8
+        bounds, acc, target = [0], 0, h2d / n_groups
+        for i, t in enumerate(host):
+            acc += t.numel() * t.element_size()
+            if acc >= target * len(bounds) and len(bounds) < n_groups:
+                bounds.append(i + 1)
+        if bounds[-1] != len(host):
+            bounds.append(len(host))
+        groups = [(bounds[j], bounds[j + 1]) for j in range(len(bounds) - 1)]
+        del opt
+        torch.cuda.empty_cache()
+        opts = [qf.FourBitAdamW(params[a:b], **HP) for a, b in groups]
+        copy_stream = torch.cuda.Stream(dev)
+        arrived = [torch.cuda.Event() for _ in groups]
+        cur = torch.cuda.current_stream(dev)
 
+        def e2e_step():
+            copy_stream.wait_stream(cur)           # the last step has finished with the gradient buffers
+            # group by group in host order: a step call begins with a small host-to-device copy of its own (the tensor
+            # table), which must not queue on the copy engine behind the gradients of the groups after it
+            for (a, b), ev, o in zip(groups, arrived, opts):
+                with torch.cuda.stream(copy_stream):
+                    for hsrc, d in zip(host[a:b], dst[a:b]):
+                        d.copy_(hsrc, non_blocking=True)
+                    ev.record(copy_stream)
+                cur.wait_event(ev)
+                o.step(grad_scale=args.grad_scale)
+            return any([o.nonfinite_seen() for o in opts])   # device -> host reads of the status words; synchronise
+
+        e2e_step()
         e2e_step()
         torch.cuda.synchronize(dev)
         t0 = time.perf_counter()
         for _ in range(k):
             e2e_step()
         dt = (time.perf_counter() - t0) / k
-        e2e = {"value": n_params / dt / 1e9, "unit": "Gparams/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
-               "ms_per_step": dt * 1e3, "steps": k}
-        del host
+        e2e = {"value": n_params / dt / 1e9, "unit": "Gparams/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * len(opts),
+               "ms_per_step": dt * 1e3, "steps": k,
+               "how": "%d groups of tensors, one optimizer each; group k steps while group k + 1 is still being copied" % len(opts)}
+        del host, opts
+        opt = None
 
     peak, peak_kind = measured_peak()
     achieved = alg_bytes / (ms_per_step * 1e-3) / 1e9
@@ -361,7 +390,35 @@ def also_block(dev, peak):
     nbytes = S.algorithmic_bytes(shapes)
     out["gpt2m"] = {"ms_per_step": ms, "first_step_ms": first, "params": S.numel(shapes), "tensors": len(shapes),
                     "GBps": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak}
-    del opt, params, grads
+    del opt
+    # the same list through the capturable step, recorded once into a CUDA graph and replayed (no host work per step)
+    for p in params:
+        p.grad = None
+    opt = qf.FourBitAdamW(params, capturable=True, **HP)
+    for p, g in zip(params, grads[0]):
+        p.grad = g
+    for _ in range(3):
+        opt.step()
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            opt.step()
+    torch.cuda.current_stream(dev).wait_stream(side)
+    for _ in range(3):
+        graph.replay()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    ev0.record()
+    for _ in range(50):
+        graph.replay()
+    ev1.record()
+    torch.cuda.synchronize(dev)
+    gms = ev0.elapsed_time(ev1) / 50
+    out["gpt2m"]["cuda_graph_replay"] = {"ms_per_step": gms, "GBps": nbytes / gms / 1e6, "frac": nbytes / gms / 1e6 / peak,
+                                         "schedule_exhausted": opt.schedule_exhausted()}
+    del opt, graph, params, grads
     torch.cuda.empty_cache()
     # Llama-13B-shaped set on one GPU (the sharded runs use it at 2, 4 and 8 GPUs)
     shapes = S.WORKLOADS["llama13b"]()
@@ -372,6 +429,15 @@ def also_block(dev, peak):
     nbytes = S.algorithmic_bytes(shapes)
     out["llama13b"] = {"ms_per_step": ms, "params": S.numel(shapes), "Gparams_per_s": S.numel(shapes) / ms / 1e6,
                        "GBps": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak}
+    del opt
+    # the same set with relaxed_update=True (an option, off by default: uncorrected bf16 parameter update, new parameters
+    # within a few bf16 units of the exact ones, codes and scales bit-identical)
+    for p in params:
+        p.grad = None
+    opt = qf.FourBitAdamW(params, relaxed_update=True, **HP)
+    timed_steps(opt, params, grads, 4, dev)
+    rms = timed_steps(opt, params, grads, 8, dev)
+    out["llama13b"]["relaxed_update"] = {"ms_per_step": rms, "GBps": nbytes / rms / 1e6, "frac": nbytes / rms / 1e6 / peak}
     del opt, params, grads
     torch.cuda.empty_cache()
     return out

@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define QF_ABI_VERSION 4
+#define QF_ABI_VERSION 5
 #define QF_BLOCK 128        /* elements per quantization block (optim/cuda_adamw_kernels.cu:431) */
 #define QF_MAX_HYPERS 16    /* hyper-parameter sets one launch can carry */
 #define QF_MAX_PEERS 15     /* peer copies of the parameter buffer one launch can feed */
@@ -57,6 +57,7 @@ typedef enum QfKind {
 
 /* Bits of the device status word (see qf_read_status). */
 #define QF_STATUS_NONFINITE 1u   /* a non-finite scale was produced (non-finite gradient or overflow) */
+#define QF_STATUS_SCHEDULE_END 2u /* qf_step_scheduled ran past the last row of a schedule whose last row does not repeat */
 
 /*
  * Scalars of one optimizer step, derived by the host in double precision and rounded once to fp32
@@ -129,6 +130,19 @@ size_t qf_workspace_bytes(int n_tensors);
 int qf_step_multi(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers,
                   void* workspace, size_t workspace_bytes, int device, void* stream);
 
+/*
+ * qf_step_multi with a cheaper parameter update for bf16 tensors on the rank-1 panel mapping (the matrices of a
+ * model: whole 2-D tensors whose column count is a multiple of 256): the square root and the two divisions of the
+ * update (optim/adamw_fourbit_triton.py:467-473) are taken as v * rsqrt(v) and multiplications by approximate
+ * reciprocals, without corrections.  The update then carries a relative error of about 2^-21, and a new bf16 parameter
+ * differs from the one qf_step_multi writes, by one bf16 unit, where the exact sum lies that close to a rounding
+ * boundary (measured: about one element in 10^5 per step).  First and second moment do not depend on the parameter,
+ * so every code and scale stays bit-identical.  All other tensors take the same path as in qf_step_multi.  An option
+ * the caller has to ask for; no counterpart in the reference.
+ */
+int qf_step_multi_relaxed(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers,
+                          void* workspace, size_t workspace_bytes, int device, void* stream);
+
 /* The two halves of qf_step_multi, for callers that must combine the new column maxima of a tensor
  * split by rows across devices (element-wise max of v_col_new over the devices that share it)
  * between them.  qf_step_pre does (1)-(2), qf_step_main does (3)-(4). No counterpart in the
@@ -137,6 +151,34 @@ int qf_step_pre(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers,
                 void* workspace, size_t workspace_bytes, int device, void* stream);
 int qf_step_main(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers,
                  void* workspace, size_t workspace_bytes, int device, void* stream);
+
+/*
+ * The step for CUDA graphs: nothing but kernel launches on `stream`, all per-step scalars resident on the device.
+ * (Asked for as a "capturable" step: the reference reads the step count back to the host every step,
+ * optim/adamw_fourbit_triton.py:458, and derives the bias corrections there; it has no counterpart of this.)
+ *
+ * qf_step_prepare writes the tensor table of `descs` into the workspace (a copy from the host: call it before the
+ * capture begins, and again whenever a descriptor changes).  qf_step_scheduled is qf_step_multi for a workspace so
+ * prepared, with the hyper-parameter sets read from device memory instead of the argument list:
+ *   device_schedule   schedule_rows x n_hypers QfHyper records, row-major; row r holds the sets of the r-th step after
+ *                     the table was written, each made by qf_make_hyper (doubles on the host: the kernels see the same
+ *                     float32 scalars as through qf_step_multi, so results are bit-identical);
+ *   device_counters   two int32: [0] the row the next step takes (the caller zeroes it when it writes the table),
+ *                     [1] the number of steps done; the call's last kernel advances both.
+ * A step past the last row takes the last row again; that is exact when the last row is stationary (constant
+ * learning rate and both bias corrections rounded to 1, i.e. after a few thousand steps at beta2 = 0.999) and is then
+ * announced with QF_SCHED_TAIL_REPEATS; without that flag such a step sets QF_STATUS_SCHEDULE_END in the status word.
+ * QF_SCHED_GRAD_SCALE: some row carries a grad_scale other than 0 / 1 (selects the kernel variant that rewrites
+ * the gradients).  The call itself may be captured into a graph: it enqueues kernels only, never copies, waits or
+ * allocates; replaying the graph repeats the step with the next row.
+ */
+#define QF_SCHED_TAIL_REPEATS 1
+#define QF_SCHED_GRAD_SCALE 2
+int qf_step_prepare(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* workspace, size_t workspace_bytes,
+                    int device, void* stream);
+int qf_step_scheduled(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* workspace,
+                      size_t workspace_bytes, int device, void* stream, const QfHyper* device_schedule,
+                      int schedule_rows, int32_t* device_counters, int flags);
 
 /*
  * qf_step_main that also stores every updated parameter into the same place of up to QF_MAX_PEERS

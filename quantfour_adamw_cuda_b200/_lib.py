@@ -11,13 +11,16 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libquantfour_b200.so")
 
-QF_ABI_VERSION = 4
+QF_ABI_VERSION = 5
 QF_MAX_HYPERS = 16
 QF_MAX_PEERS = 15
 QF_PEER_HANDLE_BYTES = 64
 QF_F32, QF_BF16 = 0, 1
 QF_KIND_FP32, QF_KIND_BLOCK, QF_KIND_RANK1 = 0, 1, 2
 QF_STATUS_NONFINITE = 1
+QF_STATUS_SCHEDULE_END = 2
+QF_SCHED_TAIL_REPEATS = 1
+QF_SCHED_GRAD_SCALE = 2
 QF_NOALLOC_MAX_ROWS_PLUS_COLS = 131072
 
 
@@ -45,8 +48,12 @@ _SIGNATURES = {
     "qf_last_error": (C.c_char_p, []),
     "qf_workspace_bytes": (C.c_size_t, [C.c_int]),
     "qf_step_multi": (C.c_int, _STEP_ARGS),
+    "qf_step_multi_relaxed": (C.c_int, _STEP_ARGS),
     "qf_step_pre": (C.c_int, _STEP_ARGS),
     "qf_step_main": (C.c_int, _STEP_ARGS),
+    "qf_step_prepare": (C.c_int, [C.POINTER(QfTensorDesc), C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]),
+    "qf_step_scheduled": (C.c_int, [C.POINTER(QfTensorDesc), C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p,
+                                    C.c_void_p, C.c_int, C.c_void_p, C.c_int]),
     "qf_step_main_push": (C.c_int, _STEP_ARGS + [C.POINTER(C.c_int64), C.c_int]),
     "qf_peer_export": (C.c_int, [C.c_void_p, C.c_int, C.c_char_p, C.POINTER(C.c_int64)]),
     "qf_peer_open": (C.c_int, [C.c_char_p, C.c_int, C.POINTER(C.c_void_p)]),

@@ -100,7 +100,7 @@ struct Plan {
 };
 
 int build_plan(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* workspace, size_t workspace_bytes,
-               int device, cudaStream_t stream, Plan* plan) {
+               int device, cudaStream_t stream, Plan* plan, bool upload = true) {
     if (n_tensors < 0) return fail(QF_ERR_BAD_ARG, "n_tensors is negative");
     if (n_tensors > 0 && !descs) return fail(QF_ERR_BAD_ARG, "descs is null");
     if (n_hypers < 1 || n_hypers > QF_MAX_HYPERS)
@@ -195,7 +195,7 @@ int build_plan(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* wor
         plan->items[k] = base[k].back();
         plan->d_base[k] = reinterpret_cast<int64_t*>(ws + kStatusBytes + tensors_bytes) + static_cast<size_t>(k) * (n + 1);
     }
-    if (n == 0) return QF_OK;
+    if (n == 0 || !upload) return QF_OK;
 
     const size_t bytes = table_bytes(n);
     std::lock_guard<std::mutex> lock(g_mu);
@@ -256,93 +256,116 @@ void roll(const Plan& pl, int mode, cudaStream_t stream) {
     qf::rank1_roll_kernel<<<pl.n * qf::kRollSlices, qf::kThreads, 0, stream>>>(pl.d_tensors, pl.n, mode);
 }
 
-template <bool SCALE>
-int launch_pre_panel(const Plan& pl, const qf::HyperPack& hp, cudaStream_t stream) {
+qf::Sched no_sched() {
+    qf::Sched sc;
+    memset(&sc, 0, sizeof sc);
+    return sc;
+}
+
+template <bool SCALE, bool SCHED>
+int launch_pre_panel(const Plan& pl, const qf::HyperPack& hp, const qf::Sched& sc, cudaStream_t stream) {
     const int dyn = qf::pre_dyn_smem(pl.any_f32_panel);
-    QF_CUDA(cudaFuncSetAttribute(qf::step_pre_kernel<true, SCALE>, cudaFuncAttributeMaxDynamicSharedMemorySize, qf::pre_dyn_smem(true)));
-    qf::step_pre_kernel<true, SCALE><<<persistent_grid(pl.items[kPrePanel], qf::kPreMinCtas), qf::kThreads, dyn, stream>>>(
-        pl.d_tensors, pl.d_base[kPrePanel], pl.n, hp, dyn / qf::kWarpsPerCta, pl.d_status);
+    QF_CUDA(cudaFuncSetAttribute(qf::step_pre_kernel<true, SCALE, SCHED>, cudaFuncAttributeMaxDynamicSharedMemorySize, qf::pre_dyn_smem(true)));
+    qf::step_pre_kernel<true, SCALE, SCHED><<<persistent_grid(pl.items[kPrePanel], qf::kPreMinCtas), qf::kThreads, dyn, stream>>>(
+        pl.d_tensors, pl.d_base[kPrePanel], pl.n, hp, dyn / qf::kWarpsPerCta, pl.d_status, sc);
     return QF_OK;
 }
 
-int launch_pre(const Plan& pl, const qf::HyperPack& hp, int n_hypers, cudaStream_t stream) {
+// `sched`: null, or the device-resident hyper-parameter table the kernels read instead of `hp`; `scaled` then says
+// whether some row of it carries a gradient scale (the host cannot look).
+int launch_pre(const Plan& pl, const qf::HyperPack& hp, int n_hypers, cudaStream_t stream, const qf::Sched* sched = nullptr,
+               bool scaled = false) {
     if (pl.n_rank1 == 0) return QF_OK;
     roll(pl, qf::kRollClear, stream);
     if (pl.items[kPrePanel]) {
-        bool scaled = false;  // the variant that rewrites the gradients runs only when some set asks for it
-        for (int k = 0; k < n_hypers; ++k) scaled = scaled || hp.h[k].gs != 1.0f;
-        if (int rc = scaled ? launch_pre_panel<true>(pl, hp, stream) : launch_pre_panel<false>(pl, hp, stream)) return rc;
+        // the variant that rewrites the gradients runs only when some set asks for it
+        if (!sched)
+            for (int k = 0; k < n_hypers; ++k) scaled = scaled || hp.h[k].gs != 1.0f;
+        int rc;
+        if (sched)
+            rc = scaled ? launch_pre_panel<true, true>(pl, hp, *sched, stream) : launch_pre_panel<false, true>(pl, hp, *sched, stream);
+        else
+            rc = scaled ? launch_pre_panel<true, false>(pl, hp, no_sched(), stream) : launch_pre_panel<false, false>(pl, hp, no_sched(), stream);
+        if (rc) return rc;
     }
-    if (pl.items[kPreFlat])
-        qf::step_pre_kernel<false><<<persistent_grid(pl.items[kPreFlat], qf::kPreMinCtas), qf::kThreads, 0, stream>>>(
-            pl.d_tensors, pl.d_base[kPreFlat], pl.n, hp, 0, pl.d_status);
+    if (pl.items[kPreFlat]) {
+        const unsigned grid = persistent_grid(pl.items[kPreFlat], qf::kPreMinCtas);
+        if (sched)
+            qf::step_pre_kernel<false, false, true><<<grid, qf::kThreads, 0, stream>>>(pl.d_tensors, pl.d_base[kPreFlat], pl.n, hp, 0,
+                                                                                     pl.d_status, *sched);
+        else
+            qf::step_pre_kernel<false><<<grid, qf::kThreads, 0, stream>>>(pl.d_tensors, pl.d_base[kPreFlat], pl.n, hp, 0, pl.d_status,
+                                                                          no_sched());
+    }
     QF_CUDA(cudaGetLastError());
     return QF_OK;
 }
 
-template <bool PUSH, bool BC1>
-int launch_main_panel(const Plan& pl, const qf::HyperPack& hp, const qf::PushPack& pp, cudaStream_t stream) {
+template <bool PUSH, bool BC1, bool SCHED, bool RELAXED = false>
+int launch_main_panel(const Plan& pl, const qf::HyperPack& hp, const qf::PushPack& pp, const qf::Sched& sc, cudaStream_t stream) {
     const int dyn = qf::main_dyn_smem(pl.any_f32_panel);
     const int ring = qf::kStages * (pl.any_f32_panel ? qf::kRowBytesF32 : qf::kRowBytesBf16);
-    QF_CUDA(cudaFuncSetAttribute(qf::step_main_kernel<true, PUSH, BC1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    QF_CUDA(cudaFuncSetAttribute(qf::step_main_kernel<true, PUSH, BC1, SCHED, RELAXED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  qf::main_dyn_smem(true)));
-    qf::step_main_kernel<true, PUSH, BC1><<<persistent_grid(pl.items[kMainPanel], qf::kMainMinCtas), qf::kThreads, dyn, stream>>>(
-        pl.d_tensors, pl.d_base[kMainPanel], pl.n, hp, ring, pl.d_status, pp);
+    qf::step_main_kernel<true, PUSH, BC1, SCHED, RELAXED><<<persistent_grid(pl.items[kMainPanel], qf::kMainMinCtas), qf::kThreads, dyn, stream>>>(
+        pl.d_tensors, pl.d_base[kMainPanel], pl.n, hp, ring, pl.d_status, pp, sc);
     return QF_OK;
 }
 
 // bc_one: every hyper-parameter set of the call has bc2s == 1 exactly (late in a run): the panel kernel then
 // runs the variant without the division by it.
+// relaxed (without peer stores only): the panel kernel whose bf16 parameter update is uncorrected.
 template <bool PUSH>
-int launch_main_kernels(const Plan& pl, const qf::HyperPack& hp, const qf::PushPack& pp, bool bc_one, cudaStream_t stream) {
+int launch_main_kernels(const Plan& pl, const qf::HyperPack& hp, const qf::PushPack& pp, bool bc_one, cudaStream_t stream,
+                        bool relaxed = false) {
     if (pl.items[kMainPanel]) {
-        if (int rc = bc_one ? launch_main_panel<PUSH, true>(pl, hp, pp, stream) : launch_main_panel<PUSH, false>(pl, hp, pp, stream))
-            return rc;
+        int rc;
+        if (!PUSH && relaxed)
+            rc = bc_one ? launch_main_panel<false, true, false, true>(pl, hp, pp, no_sched(), stream)
+                        : launch_main_panel<false, false, false, true>(pl, hp, pp, no_sched(), stream);
+        else
+            rc = bc_one ? launch_main_panel<PUSH, true, false>(pl, hp, pp, no_sched(), stream)
+                        : launch_main_panel<PUSH, false, false>(pl, hp, pp, no_sched(), stream);
+        if (rc) return rc;
     }
     if (pl.items[kMainFlat])
         qf::step_main_kernel<false, PUSH><<<persistent_grid(pl.items[kMainFlat], qf::kMainMinCtas), qf::kThreads, 0, stream>>>(
-            pl.d_tensors, pl.d_base[kMainFlat], pl.n, hp, 0, pl.d_status, pp);
+            pl.d_tensors, pl.d_base[kMainFlat], pl.n, hp, 0, pl.d_status, pp, no_sched());
     return QF_OK;
 }
 
 // `push`: null, or the peer copies of the parameter buffer the kernels also store into.
-int launch_main(const Plan& pl, const qf::HyperPack& hp, int n_hypers, cudaStream_t stream, const qf::PushPack* push = nullptr) {
+// `sched`: null, or the device-resident hyper-parameter table the kernels read instead of `hp` (no peer stores then,
+// and always the variant that divides by the bias correction: what the table holds is not known to the host).
+int launch_main(const Plan& pl, const qf::HyperPack& hp, int n_hypers, cudaStream_t stream, const qf::PushPack* push = nullptr,
+                const qf::Sched* sched = nullptr, bool relaxed = false) {
     if (pl.n == 0) return QF_OK;
     if (pl.n_rank1) roll(pl, qf::kRollRecip, stream);
     bool bc_one = true;
     for (int k = 0; k < n_hypers; ++k) bc_one = bc_one && hp.h[k].fast && hp.h[k].h.bc2s == 1.0f;
-    if (push && push->n > 0) {
+    qf::PushPack none;
+    memset(&none, 0, sizeof none);
+    if (sched) {
+        if (pl.items[kMainPanel])
+            if (int rc = launch_main_panel<false, false, true>(pl, hp, none, *sched, stream)) return rc;
+        if (pl.items[kMainFlat])
+            qf::step_main_kernel<false, false, false, true><<<persistent_grid(pl.items[kMainFlat], qf::kMainMinCtas), qf::kThreads, 0, stream>>>(
+                pl.d_tensors, pl.d_base[kMainFlat], pl.n, hp, 0, pl.d_status, none, *sched);
+    } else if (push && push->n > 0) {
         if (int rc = launch_main_kernels<true>(pl, hp, *push, bc_one, stream)) return rc;
     } else {
-        qf::PushPack none;
-        memset(&none, 0, sizeof none);
-        if (int rc = launch_main_kernels<false>(pl, hp, none, bc_one, stream)) return rc;
+        if (int rc = launch_main_kernels<false>(pl, hp, none, bc_one, stream, relaxed)) return rc;
     }
     if (pl.n_rank1) roll(pl, qf::kRollCommit, stream);
     QF_CUDA(cudaGetLastError());
     return QF_OK;
 }
 
-// The scalars as the kernels take them.  The packed sequences of the fast path need: finite scalars, an
-// eps that absorbs the square root of a denormal second moment (>= 2^-40), a bias correction whose
-// reciprocal is well defined, and a non-degenerate step size; anything else runs the exact path.
-qf::HyperDev widen_hyper(const QfHyper& h) {
-    qf::HyperDev d;
-    d.h = h;
-    d.rb = static_cast<float>(1.0 / static_cast<double>(h.bc2s));  // double rounding is harmless for 1/x
-    d.nb = -h.bc2s;
-    d.gs = h.grad_scale == 0.0f ? 1.0f : h.grad_scale;
-    const float all[] = {h.decay, h.w1, h.beta2, h.w2, h.eps, h.neg_step, h.bc2s};
-    bool ok = true;
-    for (float x : all) ok = ok && std::isfinite(x);
-    ok = ok && h.eps >= 0x1p-40f && h.eps <= 0x1p40f && h.bc2s >= 0x1p-30f && h.bc2s <= 2.0f;
-    ok = ok && std::fabs(h.neg_step) <= 0x1p40f && std::fabs(h.decay) <= 0x1p40f && h.beta2 >= 0.0f && h.w2 >= 0.0f;
-    d.fast = ok ? 1 : 0;
-    return d;
-}
+using qf::widen_hyper;
 
 int step_common(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,
-                size_t workspace_bytes, int device, void* stream, bool pre, bool main_, const qf::PushPack* push = nullptr) {
+                size_t workspace_bytes, int device, void* stream, bool pre, bool main_, const qf::PushPack* push = nullptr,
+                bool relaxed = false) {
     g_err[0] = 0;
     if (!hypers) return fail(QF_ERR_BAD_ARG, "hypers is null");
     QF_CUDA(cudaSetDevice(device));
@@ -355,7 +378,7 @@ int step_common(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers,
     if (pre)
         if (int rc = launch_pre(pl, hp, n_hypers, st)) return rc;
     if (main_)
-        if (int rc = launch_main(pl, hp, n_hypers, st, push)) return rc;
+        if (int rc = launch_main(pl, hp, n_hypers, st, push, nullptr, relaxed)) return rc;
     return QF_OK;
 }
 
@@ -400,6 +423,11 @@ int qf_step_multi(const QfTensorDesc* descs, int n_tensors, const QfHyper* hyper
     return step_common(descs, n_tensors, hypers, n_hypers, workspace, workspace_bytes, device, stream, true, true);
 }
 
+int qf_step_multi_relaxed(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,
+                          size_t workspace_bytes, int device, void* stream) {
+    return step_common(descs, n_tensors, hypers, n_hypers, workspace, workspace_bytes, device, stream, true, true, nullptr, true);
+}
+
 int qf_step_pre(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,
                 size_t workspace_bytes, int device, void* stream) {
     return step_common(descs, n_tensors, hypers, n_hypers, workspace, workspace_bytes, device, stream, true, false);
@@ -408,6 +436,40 @@ int qf_step_pre(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers,
 int qf_step_main(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,
                  size_t workspace_bytes, int device, void* stream) {
     return step_common(descs, n_tensors, hypers, n_hypers, workspace, workspace_bytes, device, stream, false, true);
+}
+
+int qf_step_prepare(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* workspace, size_t workspace_bytes, int device,
+                    void* stream) {
+    g_err[0] = 0;
+    QF_CUDA(cudaSetDevice(device));
+    Plan pl;
+    return build_plan(descs, n_tensors, n_hypers, workspace, workspace_bytes, device, static_cast<cudaStream_t>(stream), &pl);
+}
+
+int qf_step_scheduled(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* workspace, size_t workspace_bytes, int device,
+                      void* stream, const QfHyper* device_schedule, int schedule_rows, int32_t* device_counters, int flags) {
+    g_err[0] = 0;
+    if (!device_schedule || !device_counters) return fail(QF_ERR_BAD_ARG, "qf_step_scheduled: null schedule or counters");
+    if (schedule_rows < 1) return fail(QF_ERR_BAD_ARG, "qf_step_scheduled: the schedule needs at least one row");
+    if (!aligned(device_schedule, 4) || !aligned(device_counters, 4)) return fail(QF_ERR_BAD_ARG, "qf_step_scheduled: misaligned schedule or counters");
+    if (flags & ~(QF_SCHED_TAIL_REPEATS | QF_SCHED_GRAD_SCALE)) return fail(QF_ERR_BAD_ARG, "qf_step_scheduled: unknown flag bits 0x%x", flags);
+    QF_CUDA(cudaSetDevice(device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    Plan pl;   // the host half of the plan only: the tables are in the workspace already
+    if (int rc = build_plan(descs, n_tensors, n_hypers, workspace, workspace_bytes, device, st, &pl, false)) return rc;
+    if (pl.n == 0) return QF_OK;
+    qf::Sched sc;
+    sc.table = device_schedule;
+    sc.counters = device_counters;
+    sc.rows = schedule_rows;
+    sc.n_hypers = n_hypers;
+    qf::HyperPack hp;
+    memset(&hp, 0, sizeof hp);
+    if (int rc = launch_pre(pl, hp, 0, st, &sc, (flags & QF_SCHED_GRAD_SCALE) != 0)) return rc;
+    if (int rc = launch_main(pl, hp, 0, st, nullptr, &sc)) return rc;
+    qf::sched_advance_kernel<<<1, 32, 0, st>>>(device_counters, schedule_rows, (flags & QF_SCHED_TAIL_REPEATS) != 0, pl.d_status);
+    QF_CUDA(cudaGetLastError());
+    return QF_OK;
 }
 
 int qf_step_main_push(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,

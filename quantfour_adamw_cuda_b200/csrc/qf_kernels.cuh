@@ -81,6 +81,43 @@ struct HyperPack {
     HyperDev h[QF_MAX_HYPERS];
 };
 
+// The scalars as the kernels take them.  The packed sequences of the fast path need: finite scalars, an
+// eps that absorbs the square root of a denormal second moment (>= 2^-40), a bias correction whose
+// reciprocal is well defined, and a non-degenerate step size; anything else runs the exact path.
+// Host and device give the same result: the one division is an IEEE double division on both.
+__host__ __device__ inline HyperDev widen_hyper(const QfHyper& h) {
+    HyperDev d;
+    d.h = h;
+    d.rb = static_cast<float>(1.0 / static_cast<double>(h.bc2s));  // double rounding is harmless for 1/x
+    d.nb = -h.bc2s;
+    d.gs = h.grad_scale == 0.0f ? 1.0f : h.grad_scale;
+    const float all[] = {h.decay, h.w1, h.beta2, h.w2, h.eps, h.neg_step, h.bc2s};
+    bool ok = true;
+    for (float x : all) ok = ok && fabsf(x) <= 3.4028234663852886e38f;  // finite: false for NaN and infinities
+    ok = ok && h.eps >= 0x1p-40f && h.eps <= 0x1p40f && h.bc2s >= 0x1p-30f && h.bc2s <= 2.0f;
+    ok = ok && fabsf(h.neg_step) <= 0x1p40f && fabsf(h.decay) <= 0x1p40f && h.beta2 >= 0.0f && h.w2 >= 0.0f;
+    d.fast = ok ? 1 : 0;
+    return d;
+}
+
+// Hyper-parameters kept on the device, for a step that is recorded into a CUDA graph and replayed without the
+// host: `table` holds `rows` rows of `n_hypers` sets (row r = the scalars of the r-th step after the table was
+// written, derived on the host in doubles like every other set), counters[0] is the row the next step takes and
+// counters[1] counts the steps done.  A step past the last row takes the last row again.
+struct Sched {
+    const QfHyper* table;
+    const int32_t* counters;
+    int32_t rows;
+    int32_t n_hypers;
+};
+// The sets of the current row, widened, into shared memory; the caller's next __syncthreads() publishes them.
+__device__ __forceinline__ void load_sched(HyperDev* sh, const Sched& sc) {
+    if (threadIdx.x < sc.n_hypers) {
+        const int32_t r = min(max(sc.counters[0], 0), sc.rows - 1);
+        sh[threadIdx.x] = widen_hyper(sc.table[static_cast<int64_t>(r) * sc.n_hypers + threadIdx.x]);
+    }
+}
+
 // Peer copies of the parameter buffer (sharded step): every updated parameter vector is stored at
 // p + delta[k] as well, k < n, where delta[k] is the byte distance from this device's parameter buffer to
 // the mapping of peer k's buffer.  The stores ride the peer links while the update computes.
@@ -546,11 +583,22 @@ constexpr int main_dyn_smem(bool any_f32) { return kWarpsPerCta * (kStages * (an
 // The AdamW update of two elements inside the panel loop (second moment at least 2^-94, see adamw_pair).  P1: the
 // two divisions of the parameter update with one residual correction (div2_prepared1 says what that means); taken for
 // bf16 parameters only.  BC1: sqrt(1 - beta2^t) has rounded to 1, the division by it is left out.
-template <bool P1, bool BC1>
+// RELAXED (with P1 only; an option the caller has to ask for): the square root and the two divisions of the parameter
+// update are taken as v * rsqrt(v), a multiplication by RN(1 / bc2s) and a multiplication by the approximate reciprocal
+// of the denominator, without corrections.  The update then carries a relative error of about 2^-21; the new bf16
+// parameter differs from the exact one -- by one bf16 unit -- where the exact sum lies that close to a rounding
+// boundary.  m and v, hence all codes and scales, do not depend on it and stay bit-identical.
+template <bool P1, bool BC1, bool RELAXED = false>
 __device__ __forceinline__ void adamw_pair_panel(f2& p, f2 g, f2& m, f2& v, const Hyper2& h) {
     const f2 p1 = fma2(p, h.decay, bc2(0.0f));            // not a packed multiply: see adamw_pair
     m = fma2(h.w1, add2(g, neg2(m)), m);                   // m + w1 * (g - m)
     v = fma2(mul2(h.w2, g), g, mul2(h.beta2, v));          // beta2 * v + (w2 * g) * g
+    if (P1 && RELAXED) {
+        const f2 s = mul2(v, mk2(rsqrt_approx(v.x), rsqrt_approx(v.y)));   // v > 0 on this path (old maxima above zero)
+        const f2 den = BC1 ? add2(s, h.eps) : fma2(s, h.rb, h.eps);
+        p = fma2(mul2(h.nstep, m), mk2(rcp_approx(den.x), rcp_approx(den.y)), p1);
+        return;
+    }
     const f2 s = sqrt2<false>(v);
     const f2 den = add2(BC1 ? s : div2_prepared_n<P1>(s, h.rb, h.nb), h.eps);
     const f2 a = mul2(h.nstep, m);
@@ -567,7 +615,7 @@ __device__ __forceinline__ void adamw_pair_panel(f2& p, f2 g, f2& m, f2& v, cons
 // main_panel_row_exact from its unmodified inputs, after which the hot loop starts again behind it.  Rows go in
 // pairs so that the two staging slots are compile-time offsets and the per-row scalars alternate between two sets of
 // registers; an odd last row of an item takes the exact path as well.
-template <typename T, bool PUSH, bool BC1>
+template <typename T, bool PUSH, bool BC1, bool RELAXED = false>
 __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, const HyperDev& hd, const Smem& s,
                                            char* stage, int ring_bytes, uint32_t* status, const PushPack* push) {
     constexpr bool BF16 = std::is_same<T, __nv_bfloat16>::value;
@@ -660,7 +708,7 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
             const f2 ncn = (j & 1) ? mk2(b.z, b.w) : mk2(b.x, b.y);
             const f2 rcn = (j & 1) ? mk2(c.z, c.w) : mk2(c.x, c.y);
             f2 v = mul2(pair_entry(s.qv2, wv, j), mk2(fminf(row_old, co.x), fminf(row_old, co.y)));
-            adamw_pair_panel<BF16, BC1>(pp[j], gg, m[j], v, h2);
+            adamw_pair_panel<BF16, BC1, RELAXED>(pp[j], gg, m[j], v, h2);
             // requantize v: scale = min(row', col') -> -scale = max(-row', -col'), 1/scale = max(1/row', 1/col')
             const f2 nsv = mk2(fmaxf(nrow, ncn.x), fmaxf(nrow, ncn.y));
             const f2 rv = mk2(fmaxf(rrow, rcn.x), fmaxf(rrow, rcn.y));
@@ -1023,11 +1071,14 @@ __device__ __forceinline__ void main_flat(const DevTensor* tp, int64_t li, const
 // warp walks the item list with a fixed stride, so the shared-memory tables are filled once per CTA.
 constexpr int kPreMinCtas = 3;   // CTAs per SM the first pass is compiled for (80 registers)
 // SCALE (panel mapping): some hyper-parameter set of the launch carries a gradient scale other than 1.
-template <bool PANEL, bool SCALE = false>
+// SCHED: the hyper-parameter sets come from the device-resident table `sc` instead of `hp`.
+template <bool PANEL, bool SCALE = false, bool SCHED = false>
 __global__ void __launch_bounds__(kThreads, kPreMinCtas)
 step_pre_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict__ base, int n,
-                const __grid_constant__ HyperPack hp, int ring_bytes, uint32_t* status) {
+                const __grid_constant__ HyperPack hp, int ring_bytes, uint32_t* status, const __grid_constant__ Sched sc) {
     __shared__ SmemPre s;
+    __shared__ HyperDev sched_h[SCHED ? QF_MAX_HYPERS : 1];
+    if (SCHED) load_sched(sched_h, sc);
     load_smem(s);
     extern __shared__ __align__(16) char staging[];  // panel kernel: one ring of rows per warp
     char* stage = staging + (threadIdx.x >> 5) * ring_bytes;
@@ -1036,7 +1087,7 @@ step_pre_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict
         const int ti = find_tensor(base, n, item);
         const DevTensor t = tensors[ti];
         const int64_t li = item - base[ti];
-        const HyperDev& h = hp.h[t.hyper];
+        const HyperDev& h = SCHED ? sched_h[t.hyper] : hp.h[t.hyper];
         if (PANEL) {
             if (t.dtype == QF_BF16)
                 pre_panel<__nv_bfloat16, SCALE>(t, li, h, s, stage, status);
@@ -1066,13 +1117,17 @@ __device__ __forceinline__ void main_flat_dispatch(const DevTensor* tp, int64_t 
 constexpr int kMainMinCtas = 2;  // CTAs per SM the second pass is compiled for (128 registers)
 // PUSH: the launch also stores every updated parameter vector into the peers' buffers named by `pp`.
 // BC1 (panel mapping only): every hyper-parameter set of the launch has bc2s == 1.
-template <bool PANEL, bool PUSH, bool BC1 = false>
+// SCHED: the hyper-parameter sets come from the device-resident table `sc` instead of `hp`.
+// RELAXED (panel mapping, bf16 tensors): the uncorrected parameter update of adamw_pair_panel.
+template <bool PANEL, bool PUSH, bool BC1 = false, bool SCHED = false, bool RELAXED = false>
 __global__ void __launch_bounds__(kThreads, kMainMinCtas)
 step_main_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict__ base, int n,
                  const __grid_constant__ HyperPack hp, int ring_bytes, uint32_t* status,
-                 const __grid_constant__ PushPack pp) {
+                 const __grid_constant__ PushPack pp, const __grid_constant__ Sched sc) {
     const PushPack* push = PUSH ? &pp : nullptr;
     __shared__ Smem s;
+    __shared__ HyperDev sched_h[SCHED ? QF_MAX_HYPERS : 1];
+    if (SCHED) load_sched(sched_h, sc);
     load_smem(s);
     extern __shared__ __align__(16) char staging[];  // panel kernel: per warp a ring of rows plus the column block
     char* stage = staging + (threadIdx.x >> 5) * (ring_bytes + kColBytes);
@@ -1081,10 +1136,10 @@ step_main_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restric
         const int ti = find_tensor(base, n, item);
         const DevTensor* tp = tensors + ti;
         const int64_t li = item - base[ti];
-        const HyperDev& h = hp.h[tp->hyper];  // hp is a grid constant: its address is usable as it is
+        const HyperDev& h = SCHED ? sched_h[tp->hyper] : hp.h[tp->hyper];  // hp is a grid constant: its address is usable as it is
         if (PANEL) {
             if (tp->dtype == QF_BF16)
-                main_panel<__nv_bfloat16, PUSH, BC1>(tp, li, h, s, stage, ring_bytes, status, push);
+                main_panel<__nv_bfloat16, PUSH, BC1, RELAXED>(tp, li, h, s, stage, ring_bytes, status, push);
             else
                 main_panel<float, PUSH, BC1>(tp, li, h, s, stage, ring_bytes, status, push);
         } else {
@@ -1109,6 +1164,17 @@ single_tensor_kernel(const __grid_constant__ DevTensor t, const __grid_constant_
         main_flat_dispatch<__nv_bfloat16>(&t, item, h, s, &g_unread_status, nullptr);
     else
         main_flat_dispatch<float>(&t, item, h, s, &g_unread_status, nullptr);
+}
+
+// End of a step that took its hyper-parameters from a device-resident table: the next step takes the next row.
+// counters[0] stops one past the last row; a step that ran there used the last row again, which is an error
+// (reported in the status word) unless the caller said that the last row repeats for ever.
+__global__ void sched_advance_kernel(int32_t* counters, int rows, int tail_repeats, uint32_t* status) {
+    if (blockIdx.x != 0 || threadIdx.x != 0) return;
+    const int32_t r = counters[0];
+    if (r >= rows && !tail_repeats) atomicOr(status, QF_STATUS_SCHEDULE_END);
+    counters[0] = r < rows ? r + 1 : rows;
+    counters[1] += 1;
 }
 
 // Small passes over the row / column maxima of every rank-1 tensor.  One CTA per (tensor, slice).

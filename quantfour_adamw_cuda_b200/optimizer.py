@@ -91,6 +91,9 @@ class FourBitAdamW(torch.optim.Optimizer):
         *,
         fused: Optional[bool] = False,
         quant_threshold: int = DEFAULT_THRESHOLD,
+        capturable: bool = False,
+        schedule_rows: int = 1 << 18,
+        relaxed_update: bool = False,
     ):
         if not 0.0 < lr:
             raise ValueError(f"Invalid learning rate: {lr=}")
@@ -108,6 +111,15 @@ class FourBitAdamW(torch.optim.Optimizer):
         self._scratch: Dict[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]] = {}
         self._plans: Dict[Tuple[int, int], _DevicePlan] = {}
         self._fast: Optional[dict] = None
+        self.capturable = bool(capturable)
+        self.schedule_rows = int(schedule_rows)
+        # relaxed_update (not in the reference): bf16 matrices take qf_step_multi_relaxed's uncorrected parameter
+        # update -- new parameters within one bf16 unit of the exact ones, every code and scale unchanged
+        self.relaxed_update = bool(relaxed_update)
+        if self.relaxed_update and self.capturable:
+            raise ValueError("relaxed_update and capturable cannot be combined")
+        self._cap: Optional[dict] = None
+        self._status_bits = 0
 
     # ---- state ---------------------------------------------------------------------------------
 
@@ -163,6 +175,11 @@ class FourBitAdamW(torch.optim.Optimizer):
         self._scratch = {}
         self._plans = {}
         self._fast = None
+        self._cap = None
+        self.__dict__.setdefault("capturable", False)
+        self.__dict__.setdefault("schedule_rows", 1 << 18)
+        self.__dict__.setdefault("relaxed_update", False)
+        self.__dict__.setdefault("_status_bits", 0)
         state_values = list(self.state.values())
         step_is_tensor = len(state_values) != 0 and torch.is_tensor(state_values[0]["step"])
         if not step_is_tensor:
@@ -177,6 +194,7 @@ class FourBitAdamW(torch.optim.Optimizer):
         After the base class has mapped ids and restored the groups, every state entry is therefore
         re-materialised from the saved value with its saved dtype, on the parameter's device.
         """
+        self._cap = None
         super().load_state_dict(state_dict)
         saved_ids = chain.from_iterable(g["params"] for g in state_dict["param_groups"])
         params = chain.from_iterable(g["params"] for g in self.param_groups)
@@ -251,6 +269,9 @@ class FourBitAdamW(torch.optim.Optimizer):
                 loss = closure()
         self._grad_scale = 1.0 if grad_scale is None else float(grad_scale)
 
+        if self.capturable:
+            self._step_capturable()
+            return loss
         if self._fast is not None and self._step_fast():
             return loss
 
@@ -370,10 +391,14 @@ class FourBitAdamW(torch.optim.Optimizer):
             hypers.append(make_hyper(group["lr"], beta1, beta2, group["eps"], group["weight_decay"], c[1], self._grad_scale))
         dev = f["dev"]
         harr = (_lib.QfHyper * len(hypers))(*hypers)
-        rc = _lib.lib().qf_step_multi(plan.descs, len(plan.descs), harr, len(hypers), plan.workspace.data_ptr(),
+        rc = self._step_fn()(plan.descs, len(plan.descs), harr, len(hypers), plan.workspace.data_ptr(),
                                       plan.workspace.numel(), dev.index, C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
         _lib.check(rc, "qf_step_multi")
         return True
+
+    def _step_fn(self):
+        L = _lib.lib()
+        return L.qf_step_multi_relaxed if self.relaxed_update else L.qf_step_multi
 
     def _launch(self, dev: torch.device, chunk: int, entries: List[tuple], hypers: List[_lib.QfHyper], hyper_base: int) -> None:
         L = _lib.lib()
@@ -391,14 +416,13 @@ class FourBitAdamW(torch.optim.Optimizer):
             plan.descs, plan.signature = descs, signature
             plan.keepalive = [g for _, g, _, _ in entries]
         harr = (_lib.QfHyper * len(hypers))(*hypers)
-        rc = L.qf_step_multi(plan.descs, len(plan.descs), harr, len(hypers), plan.workspace.data_ptr(),
+        rc = self._step_fn()(plan.descs, len(plan.descs), harr, len(hypers), plan.workspace.data_ptr(),
                              plan.workspace.numel(), dev.index, C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
         _lib.check(rc, "qf_step_multi")
 
-    def nonfinite_seen(self) -> bool:
-        """Synchronise and report whether any step since the last call produced a non-finite scale."""
+    def _read_status(self) -> None:
+        """Synchronise, fold the status word of every workspace into `_status_bits` and clear the words."""
         L = _lib.lib()
-        seen = False
         for (dev_index, _), plan in self._plans.items():
             if plan.workspace is None:
                 continue
@@ -407,8 +431,209 @@ class FourBitAdamW(torch.optim.Optimizer):
             _lib.check(L.qf_read_status(plan.workspace.data_ptr(), dev_index,
                                         C.c_void_p(torch.cuda.current_stream(dev).cuda_stream), C.byref(word)),
                        "qf_read_status")
-            seen |= bool(word.value & _lib.QF_STATUS_NONFINITE)
+            self._status_bits |= word.value
+
+    def nonfinite_seen(self) -> bool:
+        """Synchronise and report whether any step since the last call produced a non-finite scale."""
+        self._read_status()
+        seen = bool(self._status_bits & _lib.QF_STATUS_NONFINITE)
+        self._status_bits &= ~_lib.QF_STATUS_NONFINITE
         return seen
+
+    # ---- capturable=True: a step of kernel launches only, every per-step scalar resident on the device ----------
+    #
+    # The reference reads the step count back to the host every step (adamw_fourbit_triton.py:458) and derives the
+    # bias corrections there, so its step cannot be recorded into a CUDA graph.  Here the scalars of the coming
+    # steps are derived once, on the host and in doubles exactly as `make_hyper` derives them one step at a time,
+    # into a table on the device; a device counter picks the row, the step's last kernel advances it.  The table
+    # ends where a row equals the one before it (constant learning rate, both bias corrections rounded to 1: after
+    # 17 000 steps at beta2 = 0.999), which then repeats for ever; with at most `schedule_rows` rows otherwise.
+    #
+    # Use: run one step() eagerly (it builds the tables), capture step() into a torch.cuda.CUDAGraph, replay.
+    # Gradients must live in the same buffers at every replay.  After changing a group's lr (or any other
+    # hyper-parameter) call refresh_schedule() between replays; the recorded graph stays valid.
+
+    def _cap_entries(self):
+        entries, classes, class_of = [], [], {}
+        dev = None
+        for gi, group in enumerate(self.param_groups):
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                if p.grad.is_sparse:
+                    raise RuntimeError("QuantFour AdamW does not support sparse gradients")
+                if not p.is_cuda:
+                    raise RuntimeError("FourBitAdamW needs CUDA parameters; there is no CPU path")
+                if not p.is_contiguous():
+                    raise RuntimeError("param must be contiguous")
+                if p.dtype not in _DTYPES:
+                    raise TypeError(f"parameters must be float32 or bfloat16, got {p.dtype}")
+                g = p.grad
+                if g.dtype != p.dtype or g.numel() != p.numel() or g.device != p.device:
+                    raise RuntimeError("grad must match the parameter in dtype, numel and device")
+                if not g.is_contiguous():
+                    raise RuntimeError("capturable=True needs contiguous gradients (they must stay where they are)")
+                if dev is None:
+                    dev = p.device
+                elif p.device != dev:
+                    raise RuntimeError("capturable=True needs all parameters on one device")
+                st = self.state[p]
+                if len(st) == 0:
+                    self._init_state(p)
+                key = (gi, float(st["step"]))
+                ci = class_of.get(key)
+                if ci is None:
+                    ci = class_of[key] = len(classes)
+                    classes.append(key)
+                entries.append((p, g, st, ci))
+        if len(classes) > _lib.QF_MAX_HYPERS:
+            raise RuntimeError(f"capturable=True supports at most {_lib.QF_MAX_HYPERS} (param group, step count) classes")
+        return dev, entries, classes
+
+    @staticmethod
+    def _group_key(group) -> tuple:
+        return (group["lr"], group["betas"][0], group["betas"][1], group["eps"], group["weight_decay"])
+
+    def _cap_sync_steps(self) -> None:
+        """Bring every state["step"] up to the device's count (synchronises)."""
+        cap = self._cap
+        if cap is None:
+            return
+        done = int(cap["counters"][1].item())
+        if done != cap["synced"]:
+            for (_, _, st, ci) in cap["entries"]:
+                st["step"] = torch.tensor(cap["classes"][ci][1] + done)
+            cap["synced"] = done
+
+    def _cap_write_schedule(self, cap) -> None:
+        """Rows of the coming steps for every class, from the classes' current step counts; counters := [0, 0]."""
+        import numpy as np
+        classes = cap["classes"]
+        nc = len(classes)
+        keys = [self._group_key(self.param_groups[gi]) for gi, _ in classes]
+        rows: List[List[_lib.QfHyper]] = []
+        prev = None
+        stationary = False
+        while len(rows) < self.schedule_rows:
+            r = len(rows) + 1
+            row = [make_hyper(*keys[c], classes[c][1] + r) for c in range(nc)]
+            sig = b"".join(bytes(h) for h in row)
+            rows.append(row)
+            if sig == prev:
+                stationary = True
+                break
+            prev = sig
+        flat = (_lib.QfHyper * (len(rows) * nc))(*[h for row in rows for h in row])
+        host = torch.from_numpy(np.frombuffer(flat, dtype=np.uint8).copy())
+        table = cap.get("table")
+        if table is None or table.numel() < host.numel():
+            if table is not None and cap.get("captured"):
+                raise RuntimeError("the new schedule does not fit the table a recorded graph points at; capture again")
+            table = torch.empty(max(host.numel(), 4096), dtype=torch.uint8, device=cap["dev"])
+        table[:host.numel()].copy_(host)
+        cap["table"], cap["rows"], cap["stationary"] = table, len(rows), stationary
+        cap["counters"].zero_()
+        cap["synced"] = 0
+        cap["group_keys"] = [self._group_key(g) for g in self.param_groups]
+
+    def refresh_schedule(self) -> None:
+        """Rewrite the device-resident scalars after a hyper-parameter of a group changed (call between graph
+        replays, not while capturing).  Synchronises once to read the step count."""
+        if not self.capturable or self._cap is None:
+            return
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("refresh_schedule() cannot run while a graph is being captured")
+        cap = self._cap
+        self._cap_sync_steps()
+        cap["classes"] = [(gi, t + cap["synced"]) for gi, t in cap["classes"]]
+        self._cap_write_schedule(cap)
+
+    def _cap_build(self) -> dict:
+        self._cap_sync_steps()
+        old = self._cap
+        dev, entries, classes = self._cap_entries()
+        if not entries:
+            return {"entries": [], "dev": None}
+        L = _lib.lib()
+        plan = self._plans.setdefault((dev.index, 0), _DevicePlan())
+        n = len(entries)
+        descs = (_lib.QfTensorDesc * n)()
+        for d, (p, g, st, ci) in zip(descs, entries):
+            self._fill_desc(d, p, g, st, ci)
+        need = L.qf_workspace_bytes(n)
+        if plan.workspace is None or plan.workspace.numel() < need or plan.workspace.device != dev:
+            plan.workspace = torch.zeros(need, dtype=torch.uint8, device=dev)
+        plan.descs, plan.signature, plan.keepalive = descs, None, [g for _, g, _, _ in entries]
+        stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        _lib.check(L.qf_step_prepare(descs, n, len(classes), plan.workspace.data_ptr(), plan.workspace.numel(), dev.index, stream),
+                   "qf_step_prepare")
+        cap = {
+            "dev": dev, "plan": plan, "entries": entries, "classes": classes, "captured": False,
+            "checks": [(p, p.data_ptr(), g.data_ptr()) for p, g, _, _ in entries],
+            "absent": [p for g in self.param_groups for p in g["params"] if p.grad is None],
+            "n_params": sum(len(g["params"]) for g in self.param_groups),
+            "counters": torch.zeros(2, dtype=torch.int32, device=dev),
+        }
+        if old is not None and old.get("table") is not None and old["dev"] == dev and not old.get("captured"):
+            cap["table"] = old["table"]
+        self._cap_write_schedule(cap)
+        return cap
+
+    def _cap_same_tensors(self, cap) -> bool:
+        if not cap["entries"]:
+            return all(p.grad is None for g in self.param_groups for p in g["params"])
+        if cap["n_params"] != sum(len(g["params"]) for g in self.param_groups):
+            return False
+        for p, pptr, gptr in cap["checks"]:
+            g = p.grad
+            if g is None or p.data_ptr() != pptr or g.data_ptr() != gptr:
+                return False
+        for p in cap["absent"]:
+            if p.grad is not None:
+                return False
+        return True
+
+    def _step_capturable(self) -> None:
+        if self._grad_scale != 1.0:
+            raise RuntimeError("capturable=True does not take a per-step grad_scale (the scalars of a step are fixed "
+                               "when the schedule is written)")
+        capturing = torch.cuda.is_current_stream_capturing()
+        cap = self._cap
+        same_tensors = cap is not None and self._cap_same_tensors(cap)
+        same_keys = same_tensors and cap.get("group_keys") == [self._group_key(g) for g in self.param_groups]
+        if not (same_tensors and (same_keys or not cap["entries"])):
+            if capturing:
+                raise RuntimeError("run one step() before capturing: the first step with these parameters, gradient "
+                                   "buffers and hyper-parameters builds tables on the host and copies them to the device")
+            if same_tensors:
+                self.refresh_schedule()     # only a hyper-parameter changed: same tables, new rows
+            else:
+                self._cap = self._cap_build()
+            cap = self._cap
+        if not cap["entries"]:
+            return
+        if capturing:
+            cap["captured"] = True
+        plan, dev = cap["plan"], cap["dev"]
+        flags = _lib.QF_SCHED_TAIL_REPEATS if cap["stationary"] else 0
+        rc = _lib.lib().qf_step_scheduled(plan.descs, len(plan.descs), len(cap["classes"]), plan.workspace.data_ptr(),
+                                          plan.workspace.numel(), dev.index, C.c_void_p(torch.cuda.current_stream(dev).cuda_stream),
+                                          C.c_void_p(cap["table"].data_ptr()), cap["rows"], C.c_void_p(cap["counters"].data_ptr()), flags)
+        _lib.check(rc, "qf_step_scheduled")
+
+    def schedule_exhausted(self) -> bool:
+        """capturable=True: synchronise and report whether a step ran past the last row of a schedule whose last row
+        does not repeat (more than `schedule_rows` steps without refresh_schedule() while the scalars still change)."""
+        self._read_status()
+        seen = bool(self._status_bits & _lib.QF_STATUS_SCHEDULE_END)
+        self._status_bits &= ~_lib.QF_STATUS_SCHEDULE_END
+        return seen
+
+    def state_dict(self):
+        """As torch's; with capturable=True the step counts are first read back from the device (synchronises)."""
+        if self.capturable:
+            self._cap_sync_steps()
+        return super().state_dict()
 
 
 # The reference spells the class three ways (fused_quantfour.py:12, :25; adamw_fourbit_triton.py:137).

@@ -234,3 +234,169 @@ def test_grad_scale_equals_scaling_the_gradients_first(dtype, scale):
         assert torch.equal(sa["exp_avg"], sb["exp_avg"]) and torch.equal(sa["exp_avg_sq"], sb["exp_avg_sq"])
     oa.step()       # and a step without the argument goes back to unscaled gradients
     assert not oa.nonfinite_seen()
+
+
+# ---- capturable=True: the step as kernel launches only, scalars resident on the device ------------------------
+
+def _static_problem(dtype, seed=11):
+    gen = torch.Generator().manual_seed(seed)
+    shapes = [(256, 384), (5000,), (130, 64), (64,), (128, 256)]
+    params = [nn.Parameter((torch.randn(s, generator=gen) * 0.05).to(DEV, dtype)) for s in shapes]
+    for p in params:
+        p.grad = torch.zeros_like(p)
+    return shapes, params, gen
+
+
+def _new_grads(shapes, gen, dtype, scale=1e-2):
+    return [(torch.randn(s, generator=gen) * scale).to(dtype) for s in shapes]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_capturable_step_replayed_from_a_cuda_graph_matches_the_oracle(dtype):
+    """One eager step, then the step recorded into a CUDA graph and replayed with new gradients written into the
+    same buffers: parameters, codes, scales and the step count follow the oracle bit for bit.  Two param groups."""
+    shapes, params, gen = _static_problem(dtype)
+    hp = dict(betas=(0.9, 0.99), eps=1e-8)
+    opt = qf.FourBitAdamW([{"params": params[:3], "lr": 2e-3, "weight_decay": 0.05},
+                           {"params": params[3:], "lr": 5e-4, "weight_decay": 0.0}], capturable=True, **hp)
+    cpu, states = _oracle_for(params)
+    lrs = [2e-3] * 3 + [5e-4] * 2
+    wds = [0.05] * 3 + [0.0] * 2
+
+    def feed_and_oracle():
+        gs = _new_grads(shapes, gen, dtype)
+        for p, g, c, st, lr, wd in zip(params, gs, cpu, states, lrs, wds):
+            p.grad.copy_(g)
+            CO.step_tensor(c, g, st, lr, 0.9, 0.99, 1e-8, wd)
+
+    feed_and_oracle()
+    opt.step()                                   # eager: builds the tables
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    feed_and_oracle()                            # the capture itself runs nothing; this step happens at the first replay
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            opt.step()
+    torch.cuda.current_stream().wait_stream(side)
+    graph.replay()
+    for _ in range(5):
+        feed_and_oracle()
+        graph.replay()
+    torch.cuda.synchronize()
+    opt.state_dict()                             # reads the step count back
+    _check_against_oracle(opt, params, cpu, states)
+    assert not opt.nonfinite_seen() and not opt.schedule_exhausted()
+
+
+def test_capturable_eager_steps_equal_the_plain_optimizer_and_survive_an_lr_change():
+    dtype = torch.bfloat16
+    shapes, params, gen = _static_problem(dtype, seed=12)
+    twins = [nn.Parameter(p.detach().clone()) for p in params]
+    a = qf.FourBitAdamW(params, lr=1e-3, capturable=True)
+    b = qf.FourBitAdamW(twins, lr=1e-3)
+    for it in range(9):
+        if it == 4:                              # a scheduler's doing: same tables, new rows from the current step on
+            a.param_groups[0]["lr"] = b.param_groups[0]["lr"] = 3e-4
+        for p, q, g in zip(params, twins, _new_grads(shapes, gen, dtype)):
+            p.grad.copy_(g)
+            q.grad = g.to(DEV)
+        a.step()
+        b.step()
+    sa, sb = a.state_dict()["state"], b.state_dict()["state"]
+    for i, (p, q) in enumerate(zip(params, twins)):
+        assert torch.equal(p, q)
+        assert float(sa[i]["step"]) == float(sb[i]["step"]) == 9.0
+        assert torch.equal(sa[i]["exp_avg"], sb[i]["exp_avg"]) and torch.equal(sa[i]["exp_avg_sq"], sb[i]["exp_avg_sq"])
+
+
+def test_capturable_schedule_that_runs_out_is_reported_and_refresh_continues_exactly():
+    dtype = torch.float32
+    shapes, params, gen = _static_problem(dtype, seed=13)
+    twins = [nn.Parameter(p.detach().clone()) for p in params]
+    a = qf.FourBitAdamW(params, lr=1e-3, capturable=True, schedule_rows=3)
+    b = qf.FourBitAdamW(twins, lr=1e-3)
+
+    def both(n):
+        for _ in range(n):
+            for p, q, g in zip(params, twins, _new_grads(shapes, gen, dtype)):
+                p.grad.copy_(g)
+                q.grad = g.to(DEV)
+            a.step()
+            b.step()
+
+    both(3)
+    assert not a.schedule_exhausted()
+    a.refresh_schedule()                         # rows for steps 4..6
+    both(3)
+    assert not a.schedule_exhausted()
+    for p, q in zip(params, twins):
+        assert torch.equal(p, q)
+    for p, g in zip(params, _new_grads(shapes, gen, dtype)):
+        p.grad.copy_(g)
+    a.step()                                     # a seventh step on a three-row table: takes row 3 again, and says so
+    assert a.schedule_exhausted()
+    assert float(a.state_dict()["state"][0]["step"]) == 7.0
+
+
+def test_capturable_refuses_what_it_cannot_record():
+    p = nn.Parameter(torch.zeros(64, 256, device=DEV))
+    opt = qf.FourBitAdamW([p], lr=1e-3, capturable=True)
+    p.grad = torch.zeros_like(p)
+    with pytest.raises(RuntimeError, match="grad_scale"):
+        opt.step(grad_scale=0.5)
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with pytest.raises(RuntimeError, match="before capturing"):
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                opt.step()
+    torch.cuda.synchronize()
+
+
+# ---- relaxed_update=True: uncorrected bf16 parameter update, states untouched --------------------------------
+
+def test_relaxed_update_keeps_every_code_and_scale_and_parameters_within_a_few_bf16_units():
+    """40 free-running steps of two optimizers on the same gradients, one exact, one with relaxed_update: first and
+    second moment never depend on the parameter, so codes and scales must be bit-identical throughout; a bf16
+    parameter may differ where an update fell next to a rounding boundary, and such a difference stays (as an absolute
+    amount: it counts for more units when the value shrinks later).  Counts are printed; asserted: every difference is
+    at most two bf16 units of the largest magnitude the element can have had (|p| + 40 lr), and fewer than 1 % of the
+    elements differ at all."""
+    torch.manual_seed(3)
+    lr, steps = 1e-3, 40
+    shapes = [(1024, 1024), (512, 768), (300, 256), (5000,), (64,)]
+    a = [nn.Parameter((torch.randn(s) * 0.02).to(DEV, torch.bfloat16)) for s in shapes]
+    b = [nn.Parameter(p.detach().clone()) for p in a]
+    oa = qf.FourBitAdamW(a, lr=lr)
+    ob = qf.FourBitAdamW(b, lr=lr, relaxed_update=True)
+    for _ in range(steps):
+        for p, q in zip(a, b):
+            g = (torch.randn(p.shape, device=DEV) * 1e-2).to(torch.bfloat16)
+            p.grad, q.grad = g, g.clone()
+        oa.step()
+        ob.step()
+    differ = total = 0
+    worst_units = 0.0
+    for i, (p, q) in enumerate(zip(a, b)):
+        sa, sb = oa.state[p], ob.state[q]
+        assert torch.equal(sa["exp_avg"], sb["exp_avg"]) and torch.equal(sa["exp_avg_sq"], sb["exp_avg_sq"]), i
+        if sa["momentum_qstate"]["enable"]:
+            assert torch.equal(sa["momentum_qstate"]["overhead"]["max1"], sb["momentum_qstate"]["overhead"]["max1"])
+            va, vb = sa["variance_qstate"]["overhead"], sb["variance_qstate"]["overhead"]
+            if va.get("max_dims") is not None:
+                assert torch.equal(va["max_dims"][0], vb["max_dims"][0]) and torch.equal(va["max_dims"][1], vb["max_dims"][1])
+            else:
+                assert torch.equal(va["max1"], vb["max1"])
+        pf, qf_ = p.detach().float(), q.detach().float()
+        d = (pf - qf_).abs()
+        if p.dim() != 2 or p.shape[1] % 256:
+            assert float(d.max()) == 0.0, f"tensor {i} does not take the relaxed path"
+        unit = torch.exp2(torch.floor(torch.log2(pf.abs() + steps * lr)) - 7)     # a bf16 unit at that magnitude
+        worst_units = max(worst_units, float((d / unit).max()))
+        total += d.numel()
+        differ += int((d > 0).sum())
+    print(f"relaxed update, {steps} steps: {differ} of {total} parameters differ from the exact ones; "
+          f"largest difference {worst_units:.3f} bf16 units of |p| + {steps} lr")
+    assert worst_units <= 2.0 and differ < total * 1e-2

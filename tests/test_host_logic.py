@@ -142,3 +142,12 @@ def test_step_raises_without_cuda_parameters():
     sp.grad = torch.zeros(8, 8).to_sparse()
     with pytest.raises(RuntimeError, match="sparse"):
         qf.FourBitAdamW([sp]).step()
+
+
+def test_scheduled_step_validates_its_arguments_before_touching_a_device(lib):
+    descs = (_lib.QfTensorDesc * 1)()
+    assert lib.qf_step_scheduled(descs, 1, 1, None, 0, 0, None, None, 4, None, 0) == 1 and b"null schedule" in lib.qf_last_error()
+    A = 0x10000     # never dereferenced: the checks come before any CUDA call
+    assert lib.qf_step_scheduled(descs, 1, 1, None, 0, 0, None, A, 0, A, 0) == 1 and b"at least one row" in lib.qf_last_error()
+    assert lib.qf_step_scheduled(descs, 1, 1, None, 0, 0, None, A, 4, A, 8) == 1 and b"unknown flag" in lib.qf_last_error()
+    assert lib.qf_step_scheduled(descs, 1, 1, None, 0, 0, None, A + 2, 4, A, 0) == 1 and b"misaligned" in lib.qf_last_error()
