@@ -283,6 +283,8 @@ def single_gpu(args):
         groups = [(bounds[j], bounds[j + 1]) for j in range(len(bounds) - 1)]
         del opt
         torch.cuda.empty_cache()
+        # In its steady state (same tensors, same gradient buffers) a step copies nothing from the host, so its kernels
+        # cannot get stuck on the copy engine behind the gradient copies that were submitted before it.
         opts = [qf.FourBitAdamW(params[a:b], **HP) for a, b in groups]
         copy_stream = torch.cuda.Stream(dev)
         arrived = [torch.cuda.Event() for _ in groups]
@@ -290,15 +292,13 @@ def single_gpu(args):
 
         def e2e_step():
             copy_stream.wait_stream(cur)           # the last step has finished with the gradient buffers
-            # group by group in host order: a step call begins with a small host-to-device copy of its own (the tensor
-            # table), which must not queue on the copy engine behind the gradients of the groups after it
             for (a, b), ev, o in zip(groups, arrived, opts):
                 with torch.cuda.stream(copy_stream):
                     for hsrc, d in zip(host[a:b], dst[a:b]):
                         d.copy_(hsrc, non_blocking=True)
                     ev.record(copy_stream)
                 cur.wait_event(ev)
-                o.step(grad_scale=args.grad_scale)
+                o.step()
             return any([o.nonfinite_seen() for o in opts])   # device -> host reads of the status words; synchronise
 
         e2e_step()

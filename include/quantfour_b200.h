@@ -130,19 +130,6 @@ size_t qf_workspace_bytes(int n_tensors);
 int qf_step_multi(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers,
                   void* workspace, size_t workspace_bytes, int device, void* stream);
 
-/*
- * qf_step_multi with a cheaper parameter update for bf16 tensors on the rank-1 panel mapping (the matrices of a
- * model: whole 2-D tensors whose column count is a multiple of 256): the square root and the two divisions of the
- * update (optim/adamw_fourbit_triton.py:467-473) are taken as v * rsqrt(v) and multiplications by approximate
- * reciprocals, without corrections.  The update then carries a relative error of about 2^-21, and a new bf16 parameter
- * differs from the one qf_step_multi writes, by one bf16 unit, where the exact sum lies that close to a rounding
- * boundary (measured: about one element in 10^5 per step).  First and second moment do not depend on the parameter,
- * so every code and scale stays bit-identical.  All other tensors take the same path as in qf_step_multi.  An option
- * the caller has to ask for; no counterpart in the reference.
- */
-int qf_step_multi_relaxed(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers,
-                          void* workspace, size_t workspace_bytes, int device, void* stream);
-
 /* The two halves of qf_step_multi, for callers that must combine the new column maxima of a tensor
  * split by rows across devices (element-wise max of v_col_new over the devices that share it)
  * between them.  qf_step_pre does (1)-(2), qf_step_main does (3)-(4). No counterpart in the
@@ -151,6 +138,34 @@ int qf_step_pre(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers,
                 void* workspace, size_t workspace_bytes, int device, void* stream);
 int qf_step_main(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers,
                  void* workspace, size_t workspace_bytes, int device, void* stream);
+
+/*
+ * The general form of the step calls above; they are shorthands for it.  `what` is a sum of:
+ *   QF_RUN_PRE, QF_RUN_MAIN   which halves run (both = qf_step_multi);
+ *   QF_RUN_TABLE_IN_PLACE     the workspace already holds the tensor table of exactly these `descs` (and n_hypers), written
+ *                             by qf_step_prepare or by an earlier step call on this stream, and nothing has touched the
+ *                             workspace since: the call then copies nothing from the host.  Every step call otherwise
+ *                             begins with a copy of a few tens of kilobytes on `stream`; behind long host-to-device
+ *                             copies already queued on other streams that copy, and the kernels after it, wait for them
+ *                             (measured: a step meant to overlap the arrival of the next gradients did not start
+ *                             until the last gradient had arrived);
+ *   QF_RUN_RELAXED_UPDATE     bf16 tensors on the rank-1 panel mapping (whole 2-D tensors whose column count is a multiple
+ *                             of 256) take a cheaper parameter update: the square root and the two divisions of
+ *                             optim/adamw_fourbit_triton.py:467-473 as v * rsqrt(v) and multiplications by approximate
+ *                             reciprocals, without corrections.  The update then carries a relative error of about 2^-21;
+ *                             a new bf16 parameter differs from the exact one, by one bf16 unit, where the exact sum lies
+ *                             that close to a rounding boundary (measured: 5 in 10^7 elements per step), and the
+ *                             difference stays.  The moments do not depend on the parameter: every code and scale stays
+ *                             bit-identical.  Measured gain: 4 % of a step.  Not with peer stores.
+ * peer_delta_bytes / n_peers: as for qf_step_main_push (0 peers: none).  No counterpart in the reference.
+ */
+#define QF_RUN_PRE 1
+#define QF_RUN_MAIN 2
+#define QF_RUN_TABLE_IN_PLACE 4
+#define QF_RUN_RELAXED_UPDATE 8
+int qf_step_run(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,
+                size_t workspace_bytes, int device, void* stream, int what, const int64_t* peer_delta_bytes,
+                int n_peers);
 
 /*
  * The step for CUDA graphs: nothing but kernel launches on `stream`, all per-step scalars resident on the device.

@@ -19,6 +19,7 @@ QF_F32, QF_BF16 = 0, 1
 QF_KIND_FP32, QF_KIND_BLOCK, QF_KIND_RANK1 = 0, 1, 2
 QF_STATUS_NONFINITE = 1
 QF_STATUS_SCHEDULE_END = 2
+QF_RUN_PRE, QF_RUN_MAIN, QF_RUN_TABLE_IN_PLACE, QF_RUN_RELAXED_UPDATE = 1, 2, 4, 8
 QF_SCHED_TAIL_REPEATS = 1
 QF_SCHED_GRAD_SCALE = 2
 QF_NOALLOC_MAX_ROWS_PLUS_COLS = 131072
@@ -48,7 +49,7 @@ _SIGNATURES = {
     "qf_last_error": (C.c_char_p, []),
     "qf_workspace_bytes": (C.c_size_t, [C.c_int]),
     "qf_step_multi": (C.c_int, _STEP_ARGS),
-    "qf_step_multi_relaxed": (C.c_int, _STEP_ARGS),
+    "qf_step_run": (C.c_int, _STEP_ARGS + [C.c_int, C.POINTER(C.c_int64), C.c_int]),
     "qf_step_pre": (C.c_int, _STEP_ARGS),
     "qf_step_main": (C.c_int, _STEP_ARGS),
     "qf_step_prepare": (C.c_int, [C.POINTER(QfTensorDesc), C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]),

@@ -49,10 +49,10 @@ int64_t flat_items(int64_t numel) {
 }
 
 // What the library keeps per workspace: a pair of pinned staging buffers, so that the upload of the table
-// only ever waits for the upload of the call before the previous one on the same workspace.  The table is uploaded on every call: remembering "this table is already
-// there" would be wrong as soon as the caller recycles the memory (a freed workspace whose address comes back
-// from the allocator zero-filled, with descriptors that happen to be identical), and the copy is a few tens of
-// kilobytes on the launch stream.
+// only ever waits for the upload of the call before the previous one on the same workspace.  The table is uploaded on every call unless the caller says that it is in place
+// (QF_RUN_TABLE_IN_PLACE): the library remembering "this table is already there" by itself would be wrong as soon as
+// the caller recycles the memory (a freed workspace whose address comes back from the allocator zero-filled, with
+// descriptors that happen to be identical).
 struct WsCache {
     char* pinned[2] = {nullptr, nullptr};
     cudaEvent_t ev[2] = {nullptr, nullptr};
@@ -365,13 +365,13 @@ using qf::widen_hyper;
 
 int step_common(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,
                 size_t workspace_bytes, int device, void* stream, bool pre, bool main_, const qf::PushPack* push = nullptr,
-                bool relaxed = false) {
+                bool relaxed = false, bool upload = true) {
     g_err[0] = 0;
     if (!hypers) return fail(QF_ERR_BAD_ARG, "hypers is null");
     QF_CUDA(cudaSetDevice(device));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     Plan pl;
-    if (int rc = build_plan(descs, n_tensors, n_hypers, workspace, workspace_bytes, device, st, &pl)) return rc;
+    if (int rc = build_plan(descs, n_tensors, n_hypers, workspace, workspace_bytes, device, st, &pl, upload)) return rc;
     qf::HyperPack hp;
     memset(&hp, 0, sizeof hp);
     for (int k = 0; k < n_hypers; ++k) hp.h[k] = widen_hyper(hypers[k]);
@@ -423,11 +423,6 @@ int qf_step_multi(const QfTensorDesc* descs, int n_tensors, const QfHyper* hyper
     return step_common(descs, n_tensors, hypers, n_hypers, workspace, workspace_bytes, device, stream, true, true);
 }
 
-int qf_step_multi_relaxed(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,
-                          size_t workspace_bytes, int device, void* stream) {
-    return step_common(descs, n_tensors, hypers, n_hypers, workspace, workspace_bytes, device, stream, true, true, nullptr, true);
-}
-
 int qf_step_pre(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,
                 size_t workspace_bytes, int device, void* stream) {
     return step_common(descs, n_tensors, hypers, n_hypers, workspace, workspace_bytes, device, stream, true, false);
@@ -472,11 +467,16 @@ int qf_step_scheduled(const QfTensorDesc* descs, int n_tensors, int n_hypers, vo
     return QF_OK;
 }
 
-int qf_step_main_push(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,
-                      size_t workspace_bytes, int device, void* stream, const int64_t* peer_delta_bytes, int n_peers) {
+int qf_step_run(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,
+                size_t workspace_bytes, int device, void* stream, int what, const int64_t* peer_delta_bytes, int n_peers) {
     g_err[0] = 0;
+    if (what & ~(QF_RUN_PRE | QF_RUN_MAIN | QF_RUN_TABLE_IN_PLACE | QF_RUN_RELAXED_UPDATE))
+        return fail(QF_ERR_BAD_ARG, "qf_step_run: unknown bits in `what` (0x%x)", what);
+    if (!(what & (QF_RUN_PRE | QF_RUN_MAIN))) return fail(QF_ERR_BAD_ARG, "qf_step_run: neither half of the step asked for");
     if (n_peers < 0 || n_peers > QF_MAX_PEERS) return fail(QF_ERR_BAD_ARG, "n_peers must be in 0..%d, got %d", QF_MAX_PEERS, n_peers);
     if (n_peers > 0 && !peer_delta_bytes) return fail(QF_ERR_BAD_ARG, "peer_delta_bytes is null");
+    if (n_peers > 0 && !(what & QF_RUN_MAIN)) return fail(QF_ERR_BAD_ARG, "peer stores belong to the second half of the step");
+    if (n_peers > 0 && (what & QF_RUN_RELAXED_UPDATE)) return fail(QF_ERR_BAD_ARG, "the relaxed update has no variant with peer stores");
     qf::PushPack pp;
     memset(&pp, 0, sizeof pp);
     pp.n = n_peers;
@@ -486,7 +486,15 @@ int qf_step_main_push(const QfTensorDesc* descs, int n_tensors, const QfHyper* h
             return fail(QF_ERR_BAD_ARG, "peer %d: the distance to the peer buffer must be a non-zero multiple of 16 bytes", k);
         pp.delta[k] = peer_delta_bytes[k];
     }
-    return step_common(descs, n_tensors, hypers, n_hypers, workspace, workspace_bytes, device, stream, false, true, &pp);
+    return step_common(descs, n_tensors, hypers, n_hypers, workspace, workspace_bytes, device, stream, (what & QF_RUN_PRE) != 0,
+                       (what & QF_RUN_MAIN) != 0, n_peers > 0 ? &pp : nullptr, (what & QF_RUN_RELAXED_UPDATE) != 0,
+                       !(what & QF_RUN_TABLE_IN_PLACE));
+}
+
+int qf_step_main_push(const QfTensorDesc* descs, int n_tensors, const QfHyper* hypers, int n_hypers, void* workspace,
+                      size_t workspace_bytes, int device, void* stream, const int64_t* peer_delta_bytes, int n_peers) {
+    return qf_step_run(descs, n_tensors, hypers, n_hypers, workspace, workspace_bytes, device, stream, QF_RUN_MAIN, peer_delta_bytes,
+                       n_peers);
 }
 
 // ---- sharing the parameter buffer between the processes of a node --------------------------------------------

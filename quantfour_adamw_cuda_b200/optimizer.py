@@ -5,7 +5,7 @@ and ``AdamW_QuantFour`` (optim/adamw_fourbit_triton.py:137-382): same constructo
 and ValueError checks (fused_quantfour.py:28-58), same ``step(closure)`` contract (:131-138), same
 per-parameter state keys (:61-70, :110-128).  Where the reference loops over parameters in Python and
 launches one kernel plus one device synchronisation per tensor (:171-292), this class hands the whole
-ragged parameter list to ``qf_step_multi`` once per step and never synchronises.
+ragged parameter list to ``qf_step_run`` once per step and never synchronises.
 
 State of a parameter ``p`` (what ``state_dict()`` carries):
   ``step``              0-dim float32 CPU tensor
@@ -113,7 +113,7 @@ class FourBitAdamW(torch.optim.Optimizer):
         self._fast: Optional[dict] = None
         self.capturable = bool(capturable)
         self.schedule_rows = int(schedule_rows)
-        # relaxed_update (not in the reference): bf16 matrices take qf_step_multi_relaxed's uncorrected parameter
+        # relaxed_update (not in the reference): bf16 matrices take the uncorrected parameter update (QF_RUN_RELAXED_UPDATE)
         # update -- new parameters within one bf16 unit of the exact ones, every code and scale unchanged
         self.relaxed_update = bool(relaxed_update)
         if self.relaxed_update and self.capturable:
@@ -351,7 +351,7 @@ class FourBitAdamW(torch.optim.Optimizer):
         self._fast = {
             "dev": dev, "plan": self._plans[(dev.index, 0)], "checks": [(p, p.data_ptr(), g.data_ptr()) for p, g, _, _ in entries],
             "absent": [p for g in self.param_groups for p in g["params"] if id(p) not in seen],
-            "steps_vec": steps_vec, "classes": classes,
+            "steps_vec": steps_vec, "classes": classes, "stream": torch.cuda.current_stream(dev).cuda_stream,
             "n_params": sum(len(g["params"]) for g in self.param_groups),
         }
 
@@ -391,14 +391,23 @@ class FourBitAdamW(torch.optim.Optimizer):
             hypers.append(make_hyper(group["lr"], beta1, beta2, group["eps"], group["weight_decay"], c[1], self._grad_scale))
         dev = f["dev"]
         harr = (_lib.QfHyper * len(hypers))(*hypers)
-        rc = self._step_fn()(plan.descs, len(plan.descs), harr, len(hypers), plan.workspace.data_ptr(),
-                                      plan.workspace.numel(), dev.index, C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
-        _lib.check(rc, "qf_step_multi")
+        # the table of these descriptors is in the workspace since the last call, unless a gradient moved or the step
+        # now runs on another stream than the one the table was copied on
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        self._run(plan, harr, len(hypers), dev, table_in_place=not moved and f.get("stream") == stream)
+        f["stream"] = stream
         return True
 
-    def _step_fn(self):
-        L = _lib.lib()
-        return L.qf_step_multi_relaxed if self.relaxed_update else L.qf_step_multi
+    def _run(self, plan, harr, n_hypers: int, dev: torch.device, table_in_place: bool) -> None:
+        """Both halves of the step on `plan`; `table_in_place`: the workspace holds the table of plan.descs already."""
+        what = _lib.QF_RUN_PRE | _lib.QF_RUN_MAIN
+        if self.relaxed_update:
+            what |= _lib.QF_RUN_RELAXED_UPDATE
+        if table_in_place:
+            what |= _lib.QF_RUN_TABLE_IN_PLACE
+        rc = _lib.lib().qf_step_run(plan.descs, len(plan.descs), harr, n_hypers, plan.workspace.data_ptr(), plan.workspace.numel(),
+                                    dev.index, C.c_void_p(torch.cuda.current_stream(dev).cuda_stream), what, None, 0)
+        _lib.check(rc, "qf_step_run")
 
     def _launch(self, dev: torch.device, chunk: int, entries: List[tuple], hypers: List[_lib.QfHyper], hyper_base: int) -> None:
         L = _lib.lib()
@@ -416,9 +425,7 @@ class FourBitAdamW(torch.optim.Optimizer):
             plan.descs, plan.signature = descs, signature
             plan.keepalive = [g for _, g, _, _ in entries]
         harr = (_lib.QfHyper * len(hypers))(*hypers)
-        rc = self._step_fn()(plan.descs, len(plan.descs), harr, len(hypers), plan.workspace.data_ptr(),
-                             plan.workspace.numel(), dev.index, C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
-        _lib.check(rc, "qf_step_multi")
+        self._run(plan, harr, len(hypers), dev, table_in_place=False)
 
     def _read_status(self) -> None:
         """Synchronise, fold the status word of every workspace into `_status_bits` and clear the words."""

@@ -214,6 +214,8 @@ class CudaBackend:
         self.sig = None
         self.descs = None
         self.ws: Optional[torch.Tensor] = None
+        self.generation = 0                      # counts the descriptor arrays built so far
+        self.uploaded: Optional[tuple] = None    # (generation, stream) of the table that is in the workspace
 
     def _prepare(self, states: List[RecordState]) -> None:
         sig = tuple((s.p.data_ptr(), s.g.data_ptr(), s.m.data_ptr()) for s in states)
@@ -240,26 +242,33 @@ class CudaBackend:
         if self.ws is None or self.ws.numel() < need:
             self.ws = torch.zeros(need, dtype=torch.uint8, device=dev)
         self.descs, self.sig = descs, sig
+        self.generation += 1
 
-    def _call(self, fn, states: List[RecordState], hyper: _lib.QfHyper, *extra) -> None:
+    def _call(self, what: int, states: List[RecordState], hyper: _lib.QfHyper, deltas: Sequence[int] = ()) -> None:
         if not states:
             return
         self._prepare(states)
         dev = states[0].p.device
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        # the tensor table goes up with the first call after the descriptors changed (or on a new stream); later calls
+        # say that it is in place and copy nothing
+        if self.uploaded == (self.generation, stream):
+            what |= _lib.QF_RUN_TABLE_IN_PLACE
         harr = (_lib.QfHyper * 1)(hyper)
-        _lib.check(fn(self.descs, len(self.descs), harr, 1, self.ws.data_ptr(), self.ws.numel(), dev.index,
-                      C.c_void_p(torch.cuda.current_stream(dev).cuda_stream), *extra), "sharded step")
+        arr = (C.c_int64 * len(deltas))(*deltas) if deltas else None
+        _lib.check(self.L.qf_step_run(self.descs, len(self.descs), harr, 1, self.ws.data_ptr(), self.ws.numel(), dev.index,
+                                      C.c_void_p(stream), what, arr, len(deltas)), "sharded step")
+        self.uploaded = (self.generation, stream)
 
     def pre(self, states: List[RecordState], hyper: _lib.QfHyper) -> None:
-        self._call(self.L.qf_step_pre, states, hyper)
+        self._call(_lib.QF_RUN_PRE, states, hyper)
 
     def main(self, states: List[RecordState], hyper: _lib.QfHyper) -> None:
-        self._call(self.L.qf_step_main, states, hyper)
+        self._call(_lib.QF_RUN_MAIN, states, hyper)
 
     def main_push(self, states: List[RecordState], hyper: _lib.QfHyper, deltas: Sequence[int]) -> None:
         """`main` that also stores the new parameters at the same place of every peer's flat buffer."""
-        arr = (C.c_int64 * len(deltas))(*deltas)
-        self._call(self.L.qf_step_main_push, states, hyper, arr, len(deltas))
+        self._call(_lib.QF_RUN_MAIN, states, hyper, deltas)
 
     def read_status(self) -> int:
         """Synchronise the current stream, return the status word of this backend's workspace and clear it."""
