@@ -360,6 +360,34 @@ def timed_steps(opt, params, grads, steps, dev):
     return ev0.elapsed_time(ev1) / steps
 
 
+def graph_replay_ms(params, grads, steps, dev):
+    """Device time per step of the capturable step (FourBitAdamW(capturable=True)) recorded once into a CUDA graph and
+    replayed: no host work per step.  The optimizer starts from zero state and takes three eager steps first."""
+    import quantfour_adamw_cuda_b200 as qf
+    opt = qf.FourBitAdamW(params, capturable=True, **HP)
+    for p, g in zip(params, grads):
+        p.grad = g
+    for _ in range(3):
+        opt.step()
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            opt.step()
+    torch.cuda.current_stream(dev).wait_stream(side)
+    for _ in range(3):
+        graph.replay()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    ev0.record()
+    for _ in range(steps):
+        graph.replay()
+    ev1.record()
+    torch.cuda.synchronize(dev)
+    return ev0.elapsed_time(ev1) / steps, opt.schedule_exhausted()
+
+
 def also_block(dev, peak):
     """The other configurations of the benchmark list on this GPU, outside the timed region of the headline: the
     single fp32 4096 x 4096 parameter, the stand-alone quantize / dequantize kernels, the GPT-2-medium-shaped list
@@ -376,7 +404,11 @@ def also_block(dev, peak):
     nbytes = S.algorithmic_bytes([(4096, 4096)], elem_bytes=4)
     out["fp32_4096x4096"] = {"ms_per_step": ms, "GBps": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak,
                              "algorithmic_bytes": nbytes, "note": "fp32 parameter and gradient: 14 bytes per element"}
-    del opt, p, gs
+    del opt
+    p.grad = None
+    gms, _ = graph_replay_ms([p], gs[0], 50, dev)
+    out["fp32_4096x4096"]["cuda_graph_replay"] = {"ms_per_step": gms, "GBps": nbytes / gms / 1e6, "frac": nbytes / gms / 1e6 / peak}
+    del p, gs
     # stand-alone quantize / dequantize
     out["quantize"] = quantize_kernels(dev, peak, steps=20, warmup=3)
     torch.cuda.empty_cache()
@@ -391,34 +423,10 @@ def also_block(dev, peak):
     out["gpt2m"] = {"ms_per_step": ms, "first_step_ms": first, "params": S.numel(shapes), "tensors": len(shapes),
                     "GBps": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak}
     del opt
-    # the same list through the capturable step, recorded once into a CUDA graph and replayed (no host work per step)
-    for p in params:
-        p.grad = None
-    opt = qf.FourBitAdamW(params, capturable=True, **HP)
-    for p, g in zip(params, grads[0]):
-        p.grad = g
-    for _ in range(3):
-        opt.step()
-    side = torch.cuda.Stream(dev)
-    side.wait_stream(torch.cuda.current_stream(dev))
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(side):
-        with torch.cuda.graph(graph, stream=side):
-            opt.step()
-    torch.cuda.current_stream(dev).wait_stream(side)
-    for _ in range(3):
-        graph.replay()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize(dev)
-    ev0.record()
-    for _ in range(50):
-        graph.replay()
-    ev1.record()
-    torch.cuda.synchronize(dev)
-    gms = ev0.elapsed_time(ev1) / 50
+    gms, exhausted = graph_replay_ms(params, grads[0], 50, dev)
     out["gpt2m"]["cuda_graph_replay"] = {"ms_per_step": gms, "GBps": nbytes / gms / 1e6, "frac": nbytes / gms / 1e6 / peak,
-                                         "schedule_exhausted": opt.schedule_exhausted()}
-    del opt, graph, params, grads
+                                         "schedule_exhausted": exhausted}
+    del params, grads
     torch.cuda.empty_cache()
     # Llama-13B-shaped set on one GPU (the sharded runs use it at 2, 4 and 8 GPUs)
     shapes = S.WORKLOADS["llama13b"]()

@@ -96,6 +96,9 @@ def dequantize_rank1(packed, row, col, R: int, Cc: int):
 
 def step_tensor(p: torch.Tensor, g: torch.Tensor, st: TensorState, lr, beta1, beta2, eps, weight_decay) -> None:
     """Same contract as torch_oracle.step_tensor, computed by the C library."""
+    if st.kind == "rank1nd":     # per-axis maxima over more than two axes: the torch restatement only
+        from . import torch_oracle as TO
+        return TO.step_tensor(p, g, st, lr, beta1, beta2, eps, weight_decay)
     st.step += 1
     h = _h(Hyper.make(lr, beta1, beta2, eps, weight_decay, st.step))
     n = p.numel()

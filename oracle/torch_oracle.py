@@ -124,6 +124,42 @@ def dequantize_rank1(packed: torch.Tensor, row: torch.Tensor, col: torch.Tensor,
     return QV[c].mul(torch.min(row.view(R, 1), col.view(1, C)))
 
 
+def axis_stats(v: torch.Tensor):
+    """One vector of maxima of |v| per axis, each over all the other axes (adamw_fourbit_triton.py:738-746 with
+    :1078-1087), shaped for broadcasting: [d0,1,..], [1,d1,1,..], ..."""
+    a = v.abs()
+    out = []
+    for k in range(a.dim()):
+        r = a
+        for d in range(a.dim()):
+            if d != k:
+                r = r.max(dim=d, keepdim=True).values
+        out.append(r)
+    return out
+
+
+def axis_scale(stats) -> torch.Tensor:
+    """The scale of every element: the smallest of its axes' maxima (adamw_fourbit_triton.py:749-755, :540-546)."""
+    st = stats[0].clone()
+    for s in stats[1:]:
+        st = torch.min(st, s)
+    return st
+
+
+def quantize_rank1_nd(v: torch.Tensor):
+    """Rank-1 quantize of a tensor of any rank >= 2 (adamw_fourbit_triton.py:846-856). Returns (packed, [axis maxima])."""
+    stats = axis_stats(v)
+    codes = codes_of(_safe_div(v, axis_scale(stats)), MV)
+    return pack(codes), [s.reshape(-1).clone() for s in stats]
+
+
+def dequantize_rank1_nd(packed: torch.Tensor, axes, shape) -> torch.Tensor:
+    n = math.prod(shape)
+    c = unpack(packed, n).long().view(shape)
+    stats = [a.view([-1 if d == k else 1 for d in range(len(shape))]) for k, a in enumerate(axes)]
+    return QV[c].mul(axis_scale(stats))
+
+
 def adamw_update_(p32: torch.Tensor, g32: torch.Tensor, m: torch.Tensor, v: torch.Tensor, h: Hyper) -> None:
     """The reference's update lines, operator for operator (adamw_fourbit_triton.py:415, :455-473)."""
     p32.mul_(h.decay)
@@ -140,7 +176,7 @@ def adamw_update_(p32: torch.Tensor, g32: torch.Tensor, m: torch.Tensor, v: torc
 @dataclass
 class TensorState:
     """Optimizer state of one tensor as the oracle keeps it."""
-    kind: str                      # "rank1" | "block" | "fp32"
+    kind: str                      # "rank1" | "rank1nd" (rank >= 3 with per-axis maxima: an option) | "block" | "fp32"
     shape: tuple
     step: int = 0
     m_codes: Optional[torch.Tensor] = None   # uint8 [ceil(n/2)]
@@ -149,21 +185,25 @@ class TensorState:
     v_scale: Optional[torch.Tensor] = None   # block kind: fp32 [ceil(n/128)]
     v_row: Optional[torch.Tensor] = None     # rank1 kind: fp32 [R]
     v_col: Optional[torch.Tensor] = None     # rank1 kind: fp32 [C]
+    v_axes: Optional[List[torch.Tensor]] = None   # rank1nd kind: one fp32 vector of maxima per axis
     m: Optional[torch.Tensor] = None         # fp32 kind
     v: Optional[torch.Tensor] = None
 
     @staticmethod
-    def zeros(shape, threshold: int = THRESHOLD) -> "TensorState":
+    def zeros(shape, threshold: int = THRESHOLD, nd_rank1: bool = False) -> "TensorState":
         shape = tuple(shape)
         n = math.prod(shape) if shape else 1
         if n <= threshold:      # optim/fused_quantfour.py:18-22
             return TensorState("fp32", shape, m=torch.zeros(n), v=torch.zeros(n))
         nb, nblk = (n + 1) // 2, (n + BLOCK - 1) // BLOCK
-        st = TensorState("rank1" if len(shape) == 2 else "block", shape,
+        kind = "rank1" if len(shape) == 2 else "rank1nd" if nd_rank1 and len(shape) > 2 else "block"
+        st = TensorState(kind, shape,
                          m_codes=torch.zeros(nb, dtype=torch.uint8), v_codes=torch.zeros(nb, dtype=torch.uint8),
                          m_scale=torch.zeros(nblk))
         if st.kind == "rank1":
             st.v_row, st.v_col = torch.zeros(shape[0]), torch.zeros(shape[1])
+        elif st.kind == "rank1nd":
+            st.v_axes = [torch.zeros(d) for d in shape]
         else:
             st.v_scale = torch.zeros(nblk)
         return st
@@ -176,6 +216,8 @@ class TensorState:
         m = dequantize_block(self.m_codes, self.m_scale, n, QM)
         if self.kind == "rank1":
             v = dequantize_rank1(self.v_codes, self.v_row, self.v_col, *self.shape).reshape(-1)
+        elif self.kind == "rank1nd":
+            v = dequantize_rank1_nd(self.v_codes, self.v_axes, self.shape).reshape(-1)
         else:
             v = dequantize_block(self.v_codes, self.v_scale, n, QV)
         return m, v
@@ -202,6 +244,8 @@ def step_tensor(p: torch.Tensor, g: torch.Tensor, st: TensorState, lr: float, be
     st.m_codes, st.m_scale = quantize_block(m, MM)
     if st.kind == "rank1":
         st.v_codes, st.v_row, st.v_col = quantize_rank1(v.view(st.shape))
+    elif st.kind == "rank1nd":
+        st.v_codes, st.v_axes = quantize_rank1_nd(v.view(st.shape))
     else:
         st.v_codes, st.v_scale = quantize_block(v, MV)
     assert st.m_codes.numel() == (n + 1) // 2

@@ -14,6 +14,7 @@ State of a parameter ``p`` (what ``state_dict()`` carries):
   ``momentum_qstate``   {"enable": bool, "overhead": {"max1": float32 [ceil(numel/128)]}, "qmap": None}
   ``variance_qstate``   {"enable": bool, "overhead": {...}, "qmap": None} where overhead is
                         2-D p:  {"max_dims": [float32 [R,1], float32 [1,C]], "max1": None, "dim": 2}
+                        (with nd_rank1=True also p of 3 and more dimensions: one keep-dim vector per axis)
                         else:   {"max1": float32 [ceil(numel/128)], "dim": p.dim()}
 Quantization is enabled iff ``numel > quant_threshold`` (fused_quantfour.py:18-22; threshold 4096 as in
 adamw_fourbit_triton.py:118, :128).
@@ -55,10 +56,10 @@ def make_hyper(lr: float, beta1: float, beta2: float, eps: float, weight_decay: 
                         0.0 if grad_scale == 1.0 else grad_scale)
 
 
-def state_kind(p: torch.Tensor, threshold: int) -> int:
+def state_kind(p: torch.Tensor, threshold: int, nd_rank1: bool = False) -> int:
     if not enable_param_quantization(p, threshold):
         return _lib.QF_KIND_FP32
-    return _lib.QF_KIND_RANK1 if p.dim() == 2 else _lib.QF_KIND_BLOCK
+    return _lib.QF_KIND_RANK1 if p.dim() == 2 or (nd_rank1 and p.dim() > 2) else _lib.QF_KIND_BLOCK
 
 
 class _DevicePlan:
@@ -69,6 +70,7 @@ class _DevicePlan:
         self.descs = None
         self.workspace: Optional[torch.Tensor] = None
         self.keepalive: list = []
+        self.nd: list = []      # (parameter, second-moment overhead) of the tensors of three and more dimensions with per-axis maxima
 
 
 class FourBitAdamW(torch.optim.Optimizer):
@@ -94,6 +96,7 @@ class FourBitAdamW(torch.optim.Optimizer):
         capturable: bool = False,
         schedule_rows: int = 1 << 18,
         relaxed_update: bool = False,
+        nd_rank1: bool = False,
     ):
         if not 0.0 < lr:
             raise ValueError(f"Invalid learning rate: {lr=}")
@@ -118,6 +121,13 @@ class FourBitAdamW(torch.optim.Optimizer):
         self.relaxed_update = bool(relaxed_update)
         if self.relaxed_update and self.capturable:
             raise ValueError("relaxed_update and capturable cannot be combined")
+        # nd_rank1 (the reference's scheme for every rank above one, adamw_fourbit_triton.py:841-856; off by default,
+        # where tensors of three and more dimensions take block-128 scales like vectors): the second moment of such a
+        # tensor is normalised by the smallest of its per-axis maxima.
+        self.nd_rank1 = bool(nd_rank1)
+        if self.nd_rank1 and self.capturable:
+            raise ValueError("nd_rank1 and capturable cannot be combined")
+        self._nd_rows: Dict[torch.Tensor, torch.Tensor] = {}
         self._cap: Optional[dict] = None
         self._status_bits = 0
 
@@ -138,7 +148,7 @@ class FourBitAdamW(torch.optim.Optimizer):
         self.init_qstate(p, "momentum")
         self.init_qstate(p, "variance")
         n, dev = p.numel(), p.device
-        kind = state_kind(p, self.param_quant_threshold)
+        kind = state_kind(p, self.param_quant_threshold, self.nd_rank1)
         if kind == _lib.QF_KIND_FP32:
             state["exp_avg"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.contiguous_format)
             state["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.contiguous_format)
@@ -150,9 +160,9 @@ class FourBitAdamW(torch.optim.Optimizer):
         vo = state["variance_qstate"]["overhead"]
         vo["dim"] = p.dim()
         if kind == _lib.QF_KIND_RANK1:
-            R, Cc = p.shape
-            vo["max_dims"] = [torch.zeros(R, 1, dtype=torch.float32, device=dev),
-                              torch.zeros(1, Cc, dtype=torch.float32, device=dev)]
+            # one vector of maxima per axis, shaped for broadcasting: [R,1], [1,C] for a matrix
+            vo["max_dims"] = [torch.zeros([d if k == a else 1 for k in range(p.dim())], dtype=torch.float32, device=dev)
+                              for a, d in enumerate(p.shape)]
             vo["max1"] = None
         else:
             vo["max1"] = torch.zeros(nblk, dtype=torch.float32, device=dev)
@@ -160,7 +170,7 @@ class FourBitAdamW(torch.optim.Optimizer):
     def _scratch_for(self, p: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         s = self._scratch.get(p)
         if s is None or s[0].device != p.device:
-            R, Cc = p.shape
+            R, Cc = p.numel() // p.shape[-1], p.shape[-1]
             # new maxima followed by their reciprocals (the layout qf_step_multi expects)
             s = (torch.zeros(2 * R, dtype=torch.float32, device=p.device),
                  torch.zeros(2 * Cc, dtype=torch.float32, device=p.device))
@@ -179,6 +189,8 @@ class FourBitAdamW(torch.optim.Optimizer):
         self.__dict__.setdefault("capturable", False)
         self.__dict__.setdefault("schedule_rows", 1 << 18)
         self.__dict__.setdefault("relaxed_update", False)
+        self.__dict__.setdefault("nd_rank1", False)
+        self._nd_rows = {}
         self.__dict__.setdefault("_status_bits", 0)
         state_values = list(self.state.values())
         step_is_tensor = len(state_values) != 0 and torch.is_tensor(state_values[0]["step"])
@@ -216,6 +228,7 @@ class FourBitAdamW(torch.optim.Optimizer):
         self._scratch = {}
         self._plans = {}
         self._fast = None
+        self._nd_rows = {}
 
     def dequantized_state(self, p: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """(exp_avg, exp_avg_sq) of ``p`` as float32 tensors shaped like ``p`` (dequantized on the GPU)."""
@@ -226,8 +239,8 @@ class FourBitAdamW(torch.optim.Optimizer):
         m = dequantize_m(st["exp_avg"], st["momentum_qstate"]["overhead"]["max1"], n).view(p.shape)
         vo = st["variance_qstate"]["overhead"]
         if vo.get("max_dims") is not None:
-            row, col = vo["max_dims"]
-            v = dequantize_v(st["exp_avg_sq"], row.reshape(-1), col.reshape(-1))
+            row, col = self._row_scale(p, vo), vo["max_dims"][-1]
+            v = dequantize_v(st["exp_avg_sq"], row.reshape(-1), col.reshape(-1)).view(p.shape)
         else:
             v = dequantize_v_block(st["exp_avg_sq"], vo["max1"], n).view(p.shape)
         return m, v
@@ -245,15 +258,47 @@ class FourBitAdamW(torch.optim.Optimizer):
         d.m_scale = st["momentum_qstate"]["overhead"]["max1"].data_ptr()
         vo = st["variance_qstate"]["overhead"]
         if vo.get("max_dims") is not None:
-            row, col = vo["max_dims"]
+            row, col = self._row_scale(p, vo), vo["max_dims"][-1]
             nrow, ncol = self._scratch_for(p)
             d.kind = _lib.QF_KIND_RANK1
-            d.rows, d.cols = p.shape[0], p.shape[1]
+            d.rows, d.cols = p.numel() // p.shape[-1], p.shape[-1]
             d.v_scale, d.v_col = row.data_ptr(), col.data_ptr()
             d.v_row_new, d.v_col_new = nrow.data_ptr(), ncol.data_ptr()
         else:
             d.kind = _lib.QF_KIND_BLOCK
             d.v_scale = vo["max1"].data_ptr()
+
+    # Tensors of three and more dimensions (nd_rank1=True) run through the kernels as matrices: the leading axes fold
+    # into rows, the last axis gives the columns, and the row scale of row (i0, i1, ..) is the smallest of the leading
+    # axes' maxima at i0, i1, ..: min(row scale, column maximum) is then the reference's per-axis scale.  The row scale
+    # lives in a buffer of its own (the state keeps the per-axis vectors, as the reference does).
+    def _row_scale(self, p: torch.Tensor, vo: Dict[str, Any]) -> torch.Tensor:
+        dims = vo["max_dims"]
+        if len(dims) == 2:
+            return dims[0]
+        r = self._nd_rows.get(p)
+        if r is None or r.device != p.device:
+            lead = dims[0]
+            for mx in dims[1:-1]:
+                lead = torch.minimum(lead, mx)
+            r = self._nd_rows[p] = lead.expand(*p.shape[:-1], 1).reshape(-1).contiguous()
+        return r
+
+    def _fold_new_maxima(self, p: torch.Tensor, vo: Dict[str, Any]) -> None:
+        """Between the two halves of a step: the first pass has left the new maximum of every row (a row = one index
+        tuple of the leading axes) in the scratch; the new maxima of the leading axes follow from them, go into the
+        state, and the smallest of them per row replaces the row maxima as the row scale the second pass divides by."""
+        nrow, _ = self._scratch_for(p)
+        rows = p.numel() // p.shape[-1]
+        rm = nrow[:rows].view(p.shape[:-1])
+        k = rm.dim()
+        lead = None
+        for a in range(k):
+            others = [d for d in range(k) if d != a]
+            mx = rm.amax(dim=others, keepdim=True) if others else rm
+            vo["max_dims"][a].copy_(mx.unsqueeze(-1))
+            lead = mx if lead is None else torch.minimum(lead, mx)
+        rm.copy_(lead)
 
     @torch.no_grad()
     def step(self, closure=None, *, grad_scale: Optional[float] = None):
@@ -400,14 +445,17 @@ class FourBitAdamW(torch.optim.Optimizer):
 
     def _run(self, plan, harr, n_hypers: int, dev: torch.device, table_in_place: bool) -> None:
         """Both halves of the step on `plan`; `table_in_place`: the workspace holds the table of plan.descs already."""
-        what = _lib.QF_RUN_PRE | _lib.QF_RUN_MAIN
-        if self.relaxed_update:
-            what |= _lib.QF_RUN_RELAXED_UPDATE
-        if table_in_place:
-            what |= _lib.QF_RUN_TABLE_IN_PLACE
-        rc = _lib.lib().qf_step_run(plan.descs, len(plan.descs), harr, n_hypers, plan.workspace.data_ptr(), plan.workspace.numel(),
-                                    dev.index, C.c_void_p(torch.cuda.current_stream(dev).cuda_stream), what, None, 0)
-        _lib.check(rc, "qf_step_run")
+        flags = (_lib.QF_RUN_RELAXED_UPDATE if self.relaxed_update else 0) | (_lib.QF_RUN_TABLE_IN_PLACE if table_in_place else 0)
+        L = _lib.lib()
+        args = (plan.descs, len(plan.descs), harr, n_hypers, plan.workspace.data_ptr(), plan.workspace.numel(), dev.index,
+                C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+        if not plan.nd:
+            _lib.check(L.qf_step_run(*args, _lib.QF_RUN_PRE | _lib.QF_RUN_MAIN | flags, None, 0), "qf_step_run")
+            return
+        _lib.check(L.qf_step_run(*args, _lib.QF_RUN_PRE | flags, None, 0), "qf_step_run")
+        for p, vo in plan.nd:
+            self._fold_new_maxima(p, vo)
+        _lib.check(L.qf_step_run(*args, _lib.QF_RUN_MAIN | _lib.QF_RUN_TABLE_IN_PLACE | flags, None, 0), "qf_step_run")
 
     def _launch(self, dev: torch.device, chunk: int, entries: List[tuple], hypers: List[_lib.QfHyper], hyper_base: int) -> None:
         L = _lib.lib()
@@ -424,6 +472,8 @@ class FourBitAdamW(torch.optim.Optimizer):
                 plan.workspace = torch.zeros(need, dtype=torch.uint8, device=dev)
             plan.descs, plan.signature = descs, signature
             plan.keepalive = [g for _, g, _, _ in entries]
+            plan.nd = [(p, st["variance_qstate"]["overhead"]) for p, _, st, _ in entries
+                       if st["momentum_qstate"]["enable"] and len(st["variance_qstate"]["overhead"].get("max_dims") or ()) > 2]
         harr = (_lib.QfHyper * len(hypers))(*hypers)
         self._run(plan, harr, len(hypers), dev, table_in_place=False)
 
@@ -586,19 +636,37 @@ class FourBitAdamW(torch.optim.Optimizer):
         self._cap_write_schedule(cap)
         return cap
 
-    def _cap_same_tensors(self, cap) -> bool:
+    def _cap_same_tensors(self, cap):
+        """True: same parameters and gradient buffers as when the tables were built; a list of (index, gradient): the
+        same except that these gradients live in new buffers; False: anything else."""
         if not cap["entries"]:
             return all(p.grad is None for g in self.param_groups for p in g["params"])
         if cap["n_params"] != sum(len(g["params"]) for g in self.param_groups):
             return False
-        for p, pptr, gptr in cap["checks"]:
+        moved = []
+        for i, (p, pptr, gptr) in enumerate(cap["checks"]):
             g = p.grad
-            if g is None or p.data_ptr() != pptr or g.data_ptr() != gptr:
+            if g is None or p.data_ptr() != pptr:
                 return False
+            if g.data_ptr() != gptr:
+                if not g.is_contiguous() or g.dtype != p.dtype or g.numel() != p.numel() or g.is_sparse or g.device != p.device:
+                    return False
+                moved.append((i, g))
         for p in cap["absent"]:
             if p.grad is not None:
                 return False
-        return True
+        return moved or True
+
+    def _cap_move_grads(self, cap, moved) -> None:
+        """New gradient buffers, everything else as before: only their addresses in the tensor table change."""
+        plan, dev = cap["plan"], cap["dev"]
+        for i, g in moved:
+            plan.descs[i].g = g.data_ptr()
+            plan.keepalive[i] = g
+            cap["checks"][i] = (cap["checks"][i][0], cap["checks"][i][1], g.data_ptr())
+        _lib.check(_lib.lib().qf_step_prepare(plan.descs, len(plan.descs), len(cap["classes"]), plan.workspace.data_ptr(),
+                                              plan.workspace.numel(), dev.index, C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)),
+                   "qf_step_prepare")
 
     def _step_capturable(self) -> None:
         if self._grad_scale != 1.0:
@@ -607,15 +675,18 @@ class FourBitAdamW(torch.optim.Optimizer):
         capturing = torch.cuda.is_current_stream_capturing()
         cap = self._cap
         same_tensors = cap is not None and self._cap_same_tensors(cap)
-        same_keys = same_tensors and cap.get("group_keys") == [self._group_key(g) for g in self.param_groups]
-        if not (same_tensors and (same_keys or not cap["entries"])):
+        same_keys = bool(same_tensors) and (not cap["entries"] or cap["group_keys"] == [self._group_key(g) for g in self.param_groups])
+        if not (same_tensors is True and same_keys):
             if capturing:
                 raise RuntimeError("run one step() before capturing: the first step with these parameters, gradient "
                                    "buffers and hyper-parameters builds tables on the host and copies them to the device")
-            if same_tensors:
-                self.refresh_schedule()     # only a hyper-parameter changed: same tables, new rows
-            else:
+            if not same_tensors:
                 self._cap = self._cap_build()
+            else:
+                if same_tensors is not True:
+                    self._cap_move_grads(cap, same_tensors)
+                if not same_keys:
+                    self.refresh_schedule()     # only a hyper-parameter changed: same tables, new rows
             cap = self._cap
         if not cap["entries"]:
             return

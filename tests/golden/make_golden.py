@@ -1,6 +1,7 @@
 """Generate the golden fixtures in this directory by running the reference's own Python code.
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference          (all fixtures)
+    python tests/golden/make_golden.py /path/to/reference nd       (scaling_nd.npz only)
 
 Needs the reference checkout (read-only) and no GPU.  The one reference module that holds the
 pure-PyTorch path creates a lookup table with ``device="cuda"`` at import time; it is loaded from
@@ -63,8 +64,32 @@ def edge_points(qmap: torch.Tensor, mid: torch.Tensor, seed: int) -> torch.Tenso
     ]).float()
 
 
-def main(root: str) -> None:
+def nd_scaling(ref) -> None:
+    """The reference's second-moment scaling on tensors of more than two dimensions: one vector of maxima per axis,
+    scale = the smallest of them at each element (variance_quant_scaling -> get_variance_tensor_statistics,
+    compute_variance_tensor_scale), and the scale tensor its dequantize side rebuilds from them (sqs_scale_tensor)."""
+    g = torch.Generator().manual_seed(5)
+    out = {}
+    for name, shape in (("a", (6, 20, 40)), ("b", (3, 4, 5, 16))):
+        x = (torch.randn(shape, generator=g) * 1e-3) ** 2
+        x[tuple(1 for _ in shape)] *= 1e4
+        scaled, meta = quiet(ref.variance_quant_scaling, x.clone(), x.shape)
+        assert meta["dim"] == len(shape) and meta["max1"] is None and len(meta["max_dims"]) == len(shape)
+        out[f"x_{name}"] = x.numpy()
+        out[f"scaled_{name}"] = scaled.numpy()
+        out[f"scale_{name}"] = quiet(ref.sqs_scale_tensor, meta["max_dims"]).numpy()
+        for k, mx in enumerate(meta["max_dims"]):
+            out[f"max{k}_{name}"] = mx.numpy()
+    np.savez(os.path.join(HERE, "scaling_nd.npz"), **out)
+
+
+def main(root: str, only: str = "") -> None:
     ref = load_reference(root)
+    if only == "nd":
+        nd_scaling(ref)
+        print("wrote scaling_nd.npz")
+        return
+    nd_scaling(ref)
     np.savez(os.path.join(HERE, "tables.npz"),
              qm=ref._momentum_qmap.numpy(), mm=ref._momentum_midpoint_lut.numpy(),
              qv=ref._variance_qmap.numpy(), mv=ref._variance_midpoint_lut.numpy())
@@ -141,6 +166,6 @@ def main(root: str) -> None:
 
 
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
+    if len(sys.argv) not in (2, 3):
         raise SystemExit(__doc__)
-    main(sys.argv[1])
+    main(*sys.argv[1:])     # a second argument "nd" writes scaling_nd.npz only

@@ -42,7 +42,12 @@ def _check_against_oracle(opt, params, cpu, states):
         assert torch.equal(s["exp_avg_sq"].cpu().view(torch.uint8), st.v_codes)
         assert torch.equal(s["momentum_qstate"]["overhead"]["max1"].cpu(), st.m_scale)
         vo = s["variance_qstate"]["overhead"]
-        if st.kind == "rank1":
+        if st.kind == "rank1nd":
+            assert vo["dim"] == len(st.shape) and len(vo["max_dims"]) == len(st.shape) and vo["max1"] is None
+            for k, (mx, want) in enumerate(zip(vo["max_dims"], st.v_axes)):
+                assert list(mx.shape) == [d if a == k else 1 for a, d in enumerate(st.shape)]
+                assert torch.equal(mx.cpu().reshape(-1), want), f"maxima of axis {k}"
+        elif st.kind == "rank1":
             assert vo["max_dims"][0].shape == (st.shape[0], 1) and vo["max_dims"][1].shape == (1, st.shape[1])
             assert torch.equal(vo["max_dims"][0].cpu().reshape(-1), st.v_row)
             assert torch.equal(vo["max_dims"][1].cpu().reshape(-1), st.v_col)
@@ -299,7 +304,10 @@ def test_capturable_eager_steps_equal_the_plain_optimizer_and_survive_an_lr_chan
         if it == 4:                              # a scheduler's doing: same tables, new rows from the current step on
             a.param_groups[0]["lr"] = b.param_groups[0]["lr"] = 3e-4
         for p, q, g in zip(params, twins, _new_grads(shapes, gen, dtype)):
-            p.grad.copy_(g)
+            if it in (2, 6):                     # gradients in new buffers: only their addresses are written again
+                p.grad = g.to(DEV)
+            else:
+                p.grad.copy_(g)
             q.grad = g.to(DEV)
         a.step()
         b.step()
@@ -400,3 +408,43 @@ def test_relaxed_update_keeps_every_code_and_scale_and_parameters_within_a_few_b
     print(f"relaxed update, {steps} steps: {differ} of {total} parameters differ from the exact ones; "
           f"largest difference {worst_units:.3f} bf16 units of |p| + {steps} lr")
     assert worst_units <= 2.0 and differ < total * 1e-2
+
+
+# ---- nd_rank1=True: per-axis maxima for tensors of three and more dimensions --------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_nd_rank1_follows_the_per_axis_oracle_and_round_trips_through_a_state_dict(dtype):
+    """3-D and 4-D tensors with the reference's per-axis second-moment scaling (last axis 256: panel mapping; 40 and 7:
+    flat mapping), beside a matrix, a vector and a small tensor: parameters, codes, block scales and every axis' maxima
+    against the oracle for six steps; then a state dict goes into a fresh optimizer, which continues identically."""
+    gen = torch.Generator().manual_seed(21)
+    shapes = [(6, 20, 256), (3, 4, 5, 40), (9, 11, 7, 7), (64, 256), (5000,), (4, 4, 4)]
+    cpu = [(torch.randn(s, generator=gen) * 0.05).to(dtype) for s in shapes]
+    params = [nn.Parameter(c.clone().to(DEV)) for c in cpu]
+    states = [TO.TensorState.zeros(s, nd_rank1=True) for s in shapes]
+    assert [st.kind for st in states] == ["rank1nd", "rank1nd", "rank1nd", "rank1", "block", "fp32"]
+    opt = qf.FourBitAdamW(params, lr=2e-3, weight_decay=0.02, nd_rank1=True)
+
+    def one_step(o, ps):
+        gs = [(torch.randn(s, generator=gen) * 1e-2).to(dtype) for s in shapes]
+        for p, g, c, st in zip(ps, gs, cpu, states):
+            p.grad = g.to(DEV)
+            CO.step_tensor(c, g, st, 2e-3, 0.9, 0.999, 1e-8, 0.02)
+        o.step()
+
+    for _ in range(6):
+        one_step(opt, params)
+        _check_against_oracle(opt, params, cpu, states)
+    m, v = opt.dequantized_state(params[1])
+    wm, wv = states[1].dequantized()
+    assert torch.equal(m.cpu().reshape(-1), wm) and torch.equal(v.cpu().reshape(-1), wv)
+    buf = io.BytesIO()
+    torch.save(opt.state_dict(), buf)
+    buf.seek(0)
+    params2 = [nn.Parameter(p.detach().clone()) for p in params]
+    opt2 = qf.FourBitAdamW(params2, lr=2e-3, weight_decay=0.02, nd_rank1=True)
+    opt2.load_state_dict(torch.load(buf))
+    for _ in range(3):
+        one_step(opt2, params2)
+        _check_against_oracle(opt2, params2, cpu, states)
+    assert not opt2.nonfinite_seen()

@@ -62,6 +62,42 @@ def test_scaling_helpers_match_reference():
     assert np.array_equal(xv.div(st).numpy(), z["xv_scaled"])
 
 
+def test_per_axis_scaling_of_tensors_with_more_than_two_axes_matches_reference():
+    """scaling_nd.npz: the reference's variance_quant_scaling on a 3-D and a 4-D tensor (its per-axis maxima, the
+    scaled tensor) and the scale tensor its dequantize side rebuilds from the maxima."""
+    z = _z("scaling_nd.npz")
+    for name in ("a", "b"):
+        x = torch.from_numpy(z[f"x_{name}"])
+        stats = TO.axis_stats(x)
+        for k, s in enumerate(stats):
+            assert np.array_equal(s.numpy(), z[f"max{k}_{name}"]), (name, k)
+        scale = TO.axis_scale(stats)
+        assert np.array_equal(scale.numpy(), z[f"scale_{name}"])
+        assert np.array_equal(x.div(scale).numpy(), z[f"scaled_{name}"])
+        packed, axes = TO.quantize_rank1_nd(x)
+        back = TO.dequantize_rank1_nd(packed, axes, x.shape)
+        want = TO.QV[TO.codes_of(torch.from_numpy(z[f"scaled_{name}"]), TO.MV).long()].mul(torch.from_numpy(z[f"scale_{name}"]))
+        assert torch.equal(back, want)
+
+
+def test_folding_the_leading_axes_into_rows_gives_the_same_scale():
+    """What the CUDA path relies on for rank >= 3: with the leading axes folded into rows and the per-row scale taken as
+    the smallest of the leading axes' maxima, min(row scale, column maximum) is the reference's per-axis scale."""
+    g = torch.Generator().manual_seed(0)
+    for shape in ((5, 7, 12), (2, 3, 4, 9)):
+        x = torch.rand(shape, generator=g)
+        stats = TO.axis_stats(x)
+        lead = TO.axis_scale(stats[:-1]).expand(*shape[:-1], 1).reshape(-1, 1)
+        folded = torch.min(lead, stats[-1].reshape(1, -1)).view(shape)
+        assert torch.equal(folded, TO.axis_scale(stats))
+        # and the leading axes' maxima follow from the row maxima of the folded matrix
+        rowmax = x.reshape(-1, shape[-1]).max(dim=1).values.view(shape[:-1])
+        for k in range(len(shape) - 1):
+            others = [d for d in range(len(shape) - 1) if d != k]
+            mk = rowmax.amax(dim=others) if others else rowmax
+            assert torch.equal(mk, stats[k].reshape(-1))
+
+
 @pytest.mark.parametrize("oracle", ["torch", "c"])
 def test_first_step_matches_reference_step(oracle):
     """The reference's own _single_tensor_step from zero state: scales, rank-1 maxima and the stored
