@@ -418,7 +418,7 @@ def test_nd_rank1_follows_the_per_axis_oracle_and_round_trips_through_a_state_di
     flat mapping), beside a matrix, a vector and a small tensor: parameters, codes, block scales and every axis' maxima
     against the oracle for six steps; then a state dict goes into a fresh optimizer, which continues identically."""
     gen = torch.Generator().manual_seed(21)
-    shapes = [(6, 20, 256), (3, 4, 5, 40), (9, 11, 7, 7), (64, 256), (5000,), (4, 4, 4)]
+    shapes = [(6, 20, 256), (3, 4, 10, 40), (9, 11, 7, 7), (64, 256), (5000,), (4, 4, 4)]
     cpu = [(torch.randn(s, generator=gen) * 0.05).to(dtype) for s in shapes]
     params = [nn.Parameter(c.clone().to(DEV)) for c in cpu]
     states = [TO.TensorState.zeros(s, nd_rank1=True) for s in shapes]
