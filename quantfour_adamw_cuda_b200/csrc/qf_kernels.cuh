@@ -134,14 +134,14 @@ __device__ __forceinline__ void push_store8(char* base, int64_t e, const float (
 
 // ---- first-moment search table ------------------------------------------------------------------------
 // Index = sign, exponent and two mantissa bits of x (bits 31..21).  The floats that share an index form an
-// interval that holds at most one of the 15 midpoints, so code(x) = base[index] + (thr[index] < x), with
-// thr = +inf where the interval holds none.  Built at compile time from the midpoints' bit patterns.
-struct LutEntry {
-    uint32_t thr;   // float bits
-    uint32_t base;
-};
+// interval that holds at most one of the 15 midpoints.  The table holds, per index, the number `base` of midpoints
+// below the interval; code(x) = base + (mid[base] < x): mid[base] is the smallest midpoint that is not below the
+// interval, i.e. the one inside it or one above it (then above x as well; mid[15] = +inf).  One byte per entry and the
+// threshold from the 16-entry table, which cannot have a bank conflict, instead of (threshold, count) pairs of eight
+// bytes: a warp's 32 look-ups then take about 3 shared-memory wavefronts instead of 5 (main pass -2.7 %, measured).
+// Built at compile time from the midpoints' bit patterns.
 struct Lut {
-    LutEntry e[2048];
+    alignas(16) uint8_t base[2048];
 };
 constexpr uint32_t kMidBits[15] = {0xbf466666u, 0xbf0ccccdu, 0xbea66666u, 0xbe147ae1u, 0xbd6147aeu,
                                    0xbc9ba5e3u, 0xbb343958u, 0x3b343958u, 0x3c9ba5e3u, 0x3d6147aeu,
@@ -150,26 +150,16 @@ constexpr Lut make_lut() {
     Lut t{};
     for (int idx = 0; idx < 2048; ++idx) {
         const uint32_t lo = static_cast<uint32_t>(idx & 1023) << 21, hi = lo | 0x1fffffu;  // magnitudes
-        uint32_t base = 0, thr = 0x7f800000u;
+        uint32_t base = 0;
         if (idx < 1024) {  // x >= 0: all seven negative midpoints are below
             base = 7;
-            for (int k = 7; k < 15; ++k) {
-                if (kMidBits[k] < lo)
-                    ++base;
-                else if (kMidBits[k] <= hi)
-                    thr = kMidBits[k];
-            }
+            for (int k = 7; k < 15; ++k)
+                if (kMidBits[k] < lo) ++base;
         } else {  // x < 0: a midpoint -a is below the interval [-hi, -lo] iff a > hi
-            for (int k = 0; k < 7; ++k) {
-                const uint32_t a = kMidBits[k] & 0x7fffffffu;
-                if (a > hi)
-                    ++base;
-                else if (a >= lo)
-                    thr = kMidBits[k];
-            }
+            for (int k = 0; k < 7; ++k)
+                if ((kMidBits[k] & 0x7fffffffu) > hi) ++base;
         }
-        t.e[idx].thr = thr;
-        t.e[idx].base = base;
+        t.base[idx] = static_cast<uint8_t>(base);
     }
     return t;
 }
@@ -189,13 +179,14 @@ __device__ __forceinline__ void load_smem(SmemPre& s) {
 }
 struct Smem {
     Tables t;
-    LutEntry mlut[2048];
+    alignas(16) uint8_t mlut[2048];
     float2 qm2[256];   // (qm[b & 15], qm[b >> 4])
     float2 qv2[256];   // (qv[b & 15], qv[b >> 4])
 };
 
 __device__ __forceinline__ void load_smem(Smem& s) {
-    for (int i = threadIdx.x; i < 2048; i += blockDim.x) s.mlut[i] = g_mlut.e[i];
+    for (int i = threadIdx.x; i < 512; i += blockDim.x)
+        reinterpret_cast<uint32_t*>(s.mlut)[i] = reinterpret_cast<const uint32_t*>(g_mlut.base)[i];
     for (int i = threadIdx.x; i < 256; i += blockDim.x) {
         s.qm2[i] = make_float2(c_qm[i & 15], c_qm[i >> 4]);
         s.qv2[i] = make_float2(c_qv[i & 15], c_qv[i >> 4]);
@@ -209,9 +200,10 @@ __device__ __forceinline__ f2 pair_lookup(const float2* tab, uint32_t w, int j) 
     return *reinterpret_cast<const float2*>(reinterpret_cast<const char*>(tab) + off);
 }
 
-__device__ __forceinline__ uint32_t search_m_lut(float x, const LutEntry* lut) {
-    const LutEntry e = lut[__float_as_uint(x) >> 21];
-    return e.base + (__uint_as_float(e.thr) < x ? 1u : 0u);
+// `mid`: the 15 midpoints in ascending order followed by +inf (Tables::mm).
+__device__ __forceinline__ uint32_t search_m_lut(float x, const uint8_t* lut, const float* mid) {
+    const uint32_t b = lut[__float_as_uint(x) >> 21];
+    return b + (mid[b] < x ? 1u : 0u);
 }
 
 // Second-moment map: midpoints are (1.5 + k) / 16, so the count of midpoints below x is ceil(16 x - 1.5)
@@ -358,8 +350,8 @@ __device__ __forceinline__ uint32_t quantize_m8(const f2 (&m)[4], float scale, c
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const f2 q = div2_prepared(m[j], r2, ns2);
-        w += search_m_lut(q.x, s.mlut) << (8 * j);  // disjoint nibbles: add == or, and folds into a shift-add
-        w += search_m_lut(q.y, s.mlut) << (8 * j + 4);
+        w += search_m_lut(q.x, s.mlut, s.t.mm) << (8 * j);  // disjoint nibbles: add == or, and folds into a shift-add
+        w += search_m_lut(q.y, s.mlut, s.t.mm) << (8 * j + 4);
     }
     return w;
 }
@@ -727,8 +719,8 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const f2 q = div2_prepared1(m[j], r2, ns2);
-                c[2 * j] = search_m_lut(q.x, s.mlut);
-                c[2 * j + 1] = search_m_lut(q.y, s.mlut);
+                c[2 * j] = search_m_lut(q.x, s.mlut, s.t.mm);
+                c[2 * j + 1] = search_m_lut(q.y, s.mlut, s.t.mm);
             }
             wmq = pack_u4(c[1], c[0], pack_u4(c[3], c[2], pack_u4(c[5], c[4], pack_u4(c[7], c[6], 0u))));
         }
@@ -1252,10 +1244,10 @@ quantize_block_kernel(const float* __restrict__ x, int64_t numel, uint8_t* __res
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
                         const f2 qa = div2_prepared(va[j], ra, nsa), qb = div2_prepared(vb[j], rb, nsb);
-                        wa += (MAP ? search_v_closed(qa.x) : search_m_lut(qa.x, s.mlut)) << (8 * j);
-                        wa += (MAP ? search_v_closed(qa.y) : search_m_lut(qa.y, s.mlut)) << (8 * j + 4);
-                        wb += (MAP ? search_v_closed(qb.x) : search_m_lut(qb.x, s.mlut)) << (8 * j);
-                        wb += (MAP ? search_v_closed(qb.y) : search_m_lut(qb.y, s.mlut)) << (8 * j + 4);
+                        wa += (MAP ? search_v_closed(qa.x) : search_m_lut(qa.x, s.mlut, s.t.mm)) << (8 * j);
+                        wa += (MAP ? search_v_closed(qa.y) : search_m_lut(qa.y, s.mlut, s.t.mm)) << (8 * j + 4);
+                        wb += (MAP ? search_v_closed(qb.x) : search_m_lut(qb.x, s.mlut, s.t.mm)) << (8 * j);
+                        wb += (MAP ? search_v_closed(qb.y) : search_m_lut(qb.y, s.mlut, s.t.mm)) << (8 * j + 4);
                     }
                 } else {
                     const float xa[4] = {va[0].x, va[0].y, va[1].x, va[1].y}, xb[4] = {vb[0].x, vb[0].y, vb[1].x, vb[1].y};

@@ -97,7 +97,7 @@ __global__ void k_div1(uint64_t seed, uint64_t per_thread, int mode, int a_emin,
             if (dist != 0) atomicAdd(&r->bad, 1ull);
             if (dist > 1 || dist < -1) atomicAdd(&r->checked, 1ull);
             if (codes) {
-                if (qf::search_m_lut(got[k], s.mlut) != qf::search_m_lut(want, s.mlut)) atomicAdd(&r->first_a, 1u);
+                if (qf::search_m_lut(got[k], s.mlut, s.t.mm) != qf::search_m_lut(want, s.mlut, s.t.mm)) atomicAdd(&r->first_a, 1u);
                 if (qf::search_v_closed(fabsf(got[k])) != qf::search_v_closed(fabsf(want))) atomicAdd(&r->first_b, 1u);
             }
         }
@@ -152,7 +152,7 @@ __global__ void k_search(Report* r) {
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < (1ull << 32); i += (uint64_t)gridDim.x * blockDim.x) {
         const float x = __uint_as_float((uint32_t)i);
         if (x != x) continue;  // NaN is outside the contract of the fast searches
-        if (qf::search_m_lut(x, s.mlut) != qf::search16(x, s.t.mm)) note(r, (uint32_t)i, 0);
+        if (qf::search_m_lut(x, s.mlut, s.t.mm) != qf::search16(x, s.t.mm)) note(r, (uint32_t)i, 0);
         if (qf::search_v_closed(x) != qf::search16(x, s.t.mv)) note(r, (uint32_t)i, 1);
     }
 }
