@@ -151,3 +151,15 @@ def test_scheduled_step_validates_its_arguments_before_touching_a_device(lib):
     assert lib.qf_step_scheduled(descs, 1, 1, None, 0, 0, None, A, 0, A, 0) == 1 and b"at least one row" in lib.qf_last_error()
     assert lib.qf_step_scheduled(descs, 1, 1, None, 0, 0, None, A, 4, A, 8) == 1 and b"unknown flag" in lib.qf_last_error()
     assert lib.qf_step_scheduled(descs, 1, 1, None, 0, 0, None, A + 2, 4, A, 0) == 1 and b"misaligned" in lib.qf_last_error()
+
+
+def test_general_step_call_validates_what_it_is_asked_to_do(lib):
+    descs = (_lib.QfTensorDesc * 1)()
+    hyp = (_lib.QfHyper * 1)()
+    deltas = (C.c_int64 * 1)(1024)
+    args = (descs, 1, hyp, 1, None, 0, 0, None)
+    assert lib.qf_step_run(*args, 0, None, 0) == 1 and b"neither half" in lib.qf_last_error()
+    assert lib.qf_step_run(*args, 64, None, 0) == 1 and b"unknown bits" in lib.qf_last_error()
+    assert lib.qf_step_run(*args, _lib.QF_RUN_PRE, deltas, 1) == 1 and b"second half" in lib.qf_last_error()
+    assert lib.qf_step_run(*args, _lib.QF_RUN_MAIN | _lib.QF_RUN_RELAXED_UPDATE, deltas, 1) == 1 and b"relaxed" in lib.qf_last_error()
+    assert lib.qf_step_run(*args, _lib.QF_RUN_MAIN, None, 1) == 1 and b"peer_delta_bytes" in lib.qf_last_error()
