@@ -166,7 +166,7 @@ def reference_arm(args):
     print(json.dumps({
         "impl": "reference", "metric": "4-bit AdamW step throughput", "value": value, "unit": "Gparams/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload, "sample": text},
         "cpu_baseline": {"value": value, "unit": "Gparams/s", "cores": cores, "kind": "port", "sample": text},
         "e2e": {"value": value, "unit": "Gparams/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
