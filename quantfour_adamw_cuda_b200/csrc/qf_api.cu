@@ -99,6 +99,16 @@ struct Plan {
     uint32_t* d_status = nullptr;
 };
 
+// Rows per item of the second pass over rank-1 panels: the longest of 64 / 32 / 16 that still gives every warp slot
+// of the device (two CTAs of eight warps per SM) an item; `bands64` = sum over the panel tensors of rows * panels / 64.
+int sm_count();
+int main_rows_for(int64_t items64) {
+    const int64_t slots = static_cast<int64_t>(sm_count()) * qf::kMainMinCtas * qf::kWarpsPerCta;
+    int rows = qf::kMainRowsPerItem;
+    while (rows > 16 && items64 * (qf::kMainRowsPerItem / rows) < slots) rows /= 2;
+    return rows;
+}
+
 int build_plan(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* workspace, size_t workspace_bytes,
                int device, cudaStream_t stream, Plan* plan, bool upload = true) {
     if (n_tensors < 0) return fail(QF_ERR_BAD_ARG, "n_tensors is negative");
@@ -170,6 +180,7 @@ int build_plan(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* wor
             if (panel) {
                 t.flags |= qf::kFlagPanel;
                 t.panels = static_cast<int32_t>(d.cols / qf::kPanelCols);
+                t.main_rows = qf::kMainRowsPerItem;
                 items = (d.rows + qf::kMainRowsPerItem - 1) / qf::kMainRowsPerItem * t.panels;
                 pre_items = (d.rows + qf::kPreRowsPerItem - 1) / qf::kPreRowsPerItem * t.panels;
                 if (d.dtype == QF_F32) plan->any_f32_panel = true;
@@ -185,6 +196,18 @@ int build_plan(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* wor
         tab.push_back(t);
     }
     const int n = static_cast<int>(tab.size());
+    // a small launch: shorter items in the second pass, so that the whole device takes part
+    const int main_rows = main_rows_for(base[kMainPanel].back());
+    if (main_rows != qf::kMainRowsPerItem) {
+        int64_t acc = 0;
+        for (int i = 0; i < n; ++i) {
+            if (tab[i].flags & qf::kFlagPanel) {
+                tab[i].main_rows = main_rows;
+                acc += (static_cast<int64_t>(tab[i].rows) + main_rows - 1) / main_rows * tab[i].panels;
+            }
+            base[kMainPanel][i + 1] = acc;
+        }
+    }
     plan->n = n;
     plan->n_rank1 = n_rank1;
     char* ws = static_cast<char*>(workspace);
@@ -841,7 +864,8 @@ int qf_step_rank1_noalloc(void* p, const void* g, void* m_codes, void* v_codes, 
     if (vec && t.numel < (1ll << 31) && cols % qf::kPanelCols == 0 && aligned(v_col, 16)) {
         t.flags |= qf::kFlagPanel;
         t.panels = static_cast<int32_t>(cols / qf::kPanelCols);
-        items = (rows + qf::kMainRowsPerItem - 1) / qf::kMainRowsPerItem * t.panels;
+        t.main_rows = main_rows_for((rows + qf::kMainRowsPerItem - 1) / qf::kMainRowsPerItem * t.panels);
+        items = (rows + t.main_rows - 1) / t.main_rows * t.panels;
         pre_items = (rows + qf::kPreRowsPerItem - 1) / qf::kPreRowsPerItem * t.panels;
     }
     const bool panel = t.flags & qf::kFlagPanel;

@@ -26,7 +26,9 @@ constexpr int kThreads = kWarpsPerCta * 32;
 constexpr int kPanelCols = 256;   // columns one warp covers: 32 lanes x 8 elements = two 128-blocks
 constexpr int kRowsPerItem = 16;  // rows (of kPanelCols elements) one warp work item covers
 constexpr int kMainRowsPerItem = 64;  // rows of one item of the second pass over a rank-1 panel: longer items
-                                      // amortise the per-item set-up (column maxima into shared memory)
+                                      // amortise the per-item set-up (column maxima into shared memory); a launch
+                                      // with too few such items to give every warp slot of the device one takes
+                                      // 32 or 16 rows per item instead (always an even number: rows go in pairs)
 constexpr int kPreRowsPerItem = 64;  // the same for the first pass over a rank-1 panel: each item ends with one
                                      // red.max per column, so longer items mean fewer contended atomics
 constexpr unsigned kFull = 0xffffffffu;

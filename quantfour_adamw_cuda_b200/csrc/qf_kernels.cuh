@@ -53,7 +53,7 @@ struct DevTensor {
     int32_t kind, dtype, hyper;
     int32_t flags;    // kFlagVec | kFlagPanel
     int32_t panels;   // panels per row band (cols / 256) for the panel mapping
-    int32_t pad0;
+    int32_t main_rows;  // panel mapping: rows of one item of the second pass (kMainRowsPerItem, or fewer on small launches)
     int64_t pad1[3];
 };
 static_assert(sizeof(DevTensor) == 160, "DevTensor must stay 160 bytes");
@@ -615,8 +615,8 @@ __device__ __forceinline__ void main_panel(const DevTensor* tp, int64_t li, cons
     const int lane = threadIdx.x & 31;
     const int band = static_cast<int>(li / t.panels);
     const int panel = static_cast<int>(li - static_cast<int64_t>(band) * t.panels);
-    const int r0 = band * kMainRowsPerItem;
-    const int r1 = min(r0 + kMainRowsPerItem, t.rows);
+    const int r0 = band * t.main_rows;
+    const int r1 = min(r0 + t.main_rows, t.rows);
     const int j0 = panel * kPanelCols + lane * 8;
     uint8_t* mc = reinterpret_cast<uint8_t*>(t.m);
     uint8_t* vc = reinterpret_cast<uint8_t*>(t.v);
