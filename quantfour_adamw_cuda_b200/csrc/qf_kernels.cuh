@@ -1064,6 +1064,7 @@ __device__ __forceinline__ void main_flat(const DevTensor* tp, int64_t li, const
 constexpr int kPreMinCtas = 3;   // CTAs per SM the first pass is compiled for (80 registers)
 // SCALE (panel mapping): some hyper-parameter set of the launch carries a gradient scale other than 1.
 // SCHED: the hyper-parameter sets come from the device-resident table `sc` instead of `hp`.
+// (Forms of this kernel that carry one dtype's loop only, as step_main_kernel has them, measured 5 % slower.)
 template <bool PANEL, bool SCALE = false, bool SCHED = false>
 __global__ void __launch_bounds__(kThreads, kPreMinCtas)
 step_pre_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict__ base, int n,
@@ -1111,7 +1112,9 @@ constexpr int kMainMinCtas = 2;  // CTAs per SM the second pass is compiled for 
 // BC1 (panel mapping only): every hyper-parameter set of the launch has bc2s == 1.
 // SCHED: the hyper-parameter sets come from the device-resident table `sc` instead of `hp`.
 // RELAXED (panel mapping, bf16 tensors): the uncorrected parameter update of adamw_pair_panel.
-template <bool PANEL, bool PUSH, bool BC1 = false, bool SCHED = false, bool RELAXED = false>
+// DT (panel mapping): 0 = tensors of both dtypes, 1 = the launch holds bf16 panel tensors only, 2 = fp32 only; a kernel
+// that carries one dtype's loop is scheduled a little better than one that carries both.
+template <bool PANEL, bool PUSH, bool BC1 = false, bool SCHED = false, bool RELAXED = false, int DT = 0>
 __global__ void __launch_bounds__(kThreads, kMainMinCtas)
 step_main_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict__ base, int n,
                  const __grid_constant__ HyperPack hp, int ring_bytes, uint32_t* status,
@@ -1130,7 +1133,7 @@ step_main_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restric
         const int64_t li = item - base[ti];
         const HyperDev& h = SCHED ? sched_h[tp->hyper] : hp.h[tp->hyper];  // hp is a grid constant: its address is usable as it is
         if (PANEL) {
-            if (tp->dtype == QF_BF16)
+            if (DT == 1 || (DT == 0 && tp->dtype == QF_BF16))
                 main_panel<__nv_bfloat16, PUSH, BC1, RELAXED>(tp, li, h, s, stage, ring_bytes, status, push);
             else
                 main_panel<float, PUSH, BC1>(tp, li, h, s, stage, ring_bytes, status, push);
