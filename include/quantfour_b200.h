@@ -46,7 +46,10 @@ typedef enum QfStatus {
     QF_ERR_NO_DEVICE = 4     /* no usable CUDA device / driver                              */
 } QfStatus;
 
-typedef enum QfDtype { QF_F32 = 0, QF_BF16 = 1 } QfDtype;
+/* QF_F16: IEEE half parameters and gradients (the reference's launcher dispatches half, optim/cuda_adamw_kernels.cu:443,
+ * though its kernel only handles float): widened exactly, the step runs in fp32, the new parameter is rounded to nearest
+ * even.  Tensors of this dtype take the flat mapping whatever their kind (correct, not tuned). */
+typedef enum QfDtype { QF_F32 = 0, QF_BF16 = 1, QF_F16 = 2 } QfDtype;
 
 typedef enum QfKind {
     QF_KIND_FP32 = 0,   /* moments kept in fp32 (tensors at or below the size threshold;

@@ -36,7 +36,7 @@ def _ptr(t: torch.Tensor):
 
 
 def _dtype_code(t: torch.Tensor) -> int:
-    return {torch.float32: 0, torch.bfloat16: 1}[t.dtype]
+    return {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}[t.dtype]
 
 
 def _h(h: Hyper) -> _Hyper:

@@ -15,7 +15,7 @@ QF_ABI_VERSION = 5
 QF_MAX_HYPERS = 16
 QF_MAX_PEERS = 15
 QF_PEER_HANDLE_BYTES = 64
-QF_F32, QF_BF16 = 0, 1
+QF_F32, QF_BF16, QF_F16 = 0, 1, 2
 QF_KIND_FP32, QF_KIND_BLOCK, QF_KIND_RANK1 = 0, 1, 2
 QF_STATUS_NONFINITE = 1
 QF_STATUS_SCHEDULE_END = 2

@@ -42,6 +42,8 @@ size_t table_bytes(int n) { return static_cast<size_t>(n) * sizeof(qf::DevTensor
 size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+bool valid_dtype(int dtype) { return dtype == QF_F32 || dtype == QF_BF16 || dtype == QF_F16; }
+size_t elem_size(int dtype) { return dtype == QF_F32 ? 4 : 2; }
 
 int64_t flat_items(int64_t numel) {
     const int64_t per = static_cast<int64_t>(qf::kPanelCols) * qf::kRowsPerItem;
@@ -130,11 +132,11 @@ int build_plan(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* wor
         const QfTensorDesc& d = descs[i];
         if (d.numel < 0) return fail(QF_ERR_BAD_ARG, "tensor %d: negative numel", i);
         if (d.numel == 0) continue;
-        if (d.dtype != QF_F32 && d.dtype != QF_BF16) return fail(QF_ERR_BAD_ARG, "tensor %d: bad dtype %d", i, d.dtype);
+        if (!valid_dtype(d.dtype)) return fail(QF_ERR_BAD_ARG, "tensor %d: bad dtype %d", i, d.dtype);
         if (d.kind < QF_KIND_FP32 || d.kind > QF_KIND_RANK1) return fail(QF_ERR_BAD_ARG, "tensor %d: bad kind %d", i, d.kind);
         if (d.hyper < 0 || d.hyper >= n_hypers) return fail(QF_ERR_BAD_ARG, "tensor %d: hyper index %d out of range", i, d.hyper);
         if (!d.p || !d.g || !d.m || !d.v) return fail(QF_ERR_BAD_ARG, "tensor %d: null p/g/m/v pointer", i);
-        const size_t esz = d.dtype == QF_BF16 ? 2 : 4;
+        const size_t esz = elem_size(d.dtype);
         if (!aligned(d.p, esz) || !aligned(d.g, esz)) return fail(QF_ERR_BAD_ARG, "tensor %d: p/g not element-aligned", i);
         qf::DevTensor t;
         memset(&t, 0, sizeof t);
@@ -176,7 +178,7 @@ int build_plan(const QfTensorDesc* descs, int n_tensors, int n_hypers, void* wor
             t.flat_off = d.flat_offset;
             if (!aligned(t.vrow_rcp, 4) || !aligned(t.vcol_rcp, 4)) return fail(QF_ERR_BAD_ARG, "tensor %d: rank-1 buffers misaligned", i);
             const bool whole = d.flat_offset == 0 && d.rows * d.cols == d.numel;
-            const bool panel = whole && d.numel < (1ll << 31) && vec && d.cols % qf::kPanelCols == 0 && aligned(d.v_col, 16) && aligned(d.v_col_new, 16) &&
+            const bool panel = whole && d.dtype != QF_F16 && d.numel < (1ll << 31) && vec && d.cols % qf::kPanelCols == 0 && aligned(d.v_col, 16) && aligned(d.v_col_new, 16) &&
                                aligned(t.vcol_rcp, 16);
             if (panel) {
                 t.flags |= qf::kFlagPanel;
@@ -653,11 +655,11 @@ int qf_fused_4bit(void* p, const void* g, void* exp, void* sq, float* exp_scale,
                   int dtype, double beta1, double beta2, double lr, double weight_decay, double eps, double step,
                   int device, void* stream) {
     g_err[0] = 0;
-    if (dtype != QF_F32 && dtype != QF_BF16) return fail(QF_ERR_BAD_ARG, "bad dtype %d", dtype);
+    if (!valid_dtype(dtype)) return fail(QF_ERR_BAD_ARG, "bad dtype %d", dtype);
     if (numel < 0) return fail(QF_ERR_BAD_ARG, "negative numel");
     if (numel == 0) return QF_OK;
     if (!p || !g || !exp || !sq || !exp_scale || !sq_scale) return fail(QF_ERR_BAD_ARG, "null pointer");
-    if (!aligned(p, dtype == QF_BF16 ? 2 : 4) || !aligned(g, dtype == QF_BF16 ? 2 : 4) || !aligned(exp_scale, 4) || !aligned(sq_scale, 4))
+    if (!aligned(p, elem_size(dtype)) || !aligned(g, elem_size(dtype)) || !aligned(exp_scale, 4) || !aligned(sq_scale, 4))
         return fail(QF_ERR_BAD_ARG, "qf_fused_4bit: p / g not element-aligned or scales not 4-byte aligned");
     QF_CUDA(cudaSetDevice(device));
     qf::DevTensor t;
@@ -684,11 +686,11 @@ int qf_fused_single_tensor(void* p, const void* g, float* exp_avg, float* exp_av
                            double beta1, double beta2, double lr, double weight_decay, double eps, double step,
                            int device, void* stream) {
     g_err[0] = 0;
-    if (dtype != QF_F32 && dtype != QF_BF16) return fail(QF_ERR_BAD_ARG, "bad dtype %d", dtype);
+    if (!valid_dtype(dtype)) return fail(QF_ERR_BAD_ARG, "bad dtype %d", dtype);
     if (numel < 0) return fail(QF_ERR_BAD_ARG, "negative numel");
     if (numel == 0) return QF_OK;
     if (!p || !g || !exp_avg || !exp_avg_sq) return fail(QF_ERR_BAD_ARG, "null pointer");
-    if (!aligned(p, dtype == QF_BF16 ? 2 : 4) || !aligned(g, dtype == QF_BF16 ? 2 : 4) || !aligned(exp_avg, 4) || !aligned(exp_avg_sq, 4))
+    if (!aligned(p, elem_size(dtype)) || !aligned(g, elem_size(dtype)) || !aligned(exp_avg, 4) || !aligned(exp_avg_sq, 4))
         return fail(QF_ERR_BAD_ARG, "qf_fused_single_tensor: p / g not element-aligned or moments not 4-byte aligned");
     QF_CUDA(cudaSetDevice(device));
     qf::DevTensor t;
@@ -830,13 +832,13 @@ int qf_step_rank1_noalloc(void* p, const void* g, void* m_codes, void* v_codes, 
                           void* stream) {
     g_err[0] = 0;
     if (!hyper) return fail(QF_ERR_BAD_ARG, "hyper is null");
-    if (dtype != QF_F32 && dtype != QF_BF16) return fail(QF_ERR_BAD_ARG, "bad dtype %d", dtype);
+    if (!valid_dtype(dtype)) return fail(QF_ERR_BAD_ARG, "bad dtype %d", dtype);
     if (rows <= 0 || cols <= 0) return fail(QF_ERR_BAD_ARG, "rows and cols must be positive");
     if (rows + cols > QF_NOALLOC_MAX_ROWS_PLUS_COLS)
         return fail(QF_ERR_BAD_ARG, "rows + cols = %lld exceeds the built-in scratch (QF_NOALLOC_MAX_ROWS_PLUS_COLS = %d); use qf_step_multi with caller-owned scratch",
                     (long long)(rows + cols), QF_NOALLOC_MAX_ROWS_PLUS_COLS);
     if (!p || !g || !m_codes || !v_codes || !m_scale || !v_row || !v_col) return fail(QF_ERR_BAD_ARG, "null pointer");
-    const size_t esz = dtype == QF_BF16 ? 2 : 4;
+    const size_t esz = elem_size(dtype);
     if (!aligned(p, esz) || !aligned(g, esz) || !aligned(m_scale, 4) || !aligned(v_row, 4) || !aligned(v_col, 4))
         return fail(QF_ERR_BAD_ARG, "buffer not element-aligned");
     QF_CUDA(cudaSetDevice(device));
@@ -871,7 +873,7 @@ int qf_step_rank1_noalloc(void* p, const void* g, void* m_codes, void* v_codes, 
     const bool vec = aligned(p, 16) && aligned(g, 16) && aligned(m_codes, 4) && aligned(v_codes, 4);
     if (vec) t.flags |= qf::kFlagVec;
     int64_t items = flat_items(t.numel), pre_items = items;
-    if (vec && t.numel < (1ll << 31) && cols % qf::kPanelCols == 0 && aligned(v_col, 16)) {
+    if (vec && dtype != QF_F16 && t.numel < (1ll << 31) && cols % qf::kPanelCols == 0 && aligned(v_col, 16)) {
         t.flags |= qf::kFlagPanel;
         t.panels = static_cast<int32_t>(cols / qf::kPanelCols);
         t.main_rows = main_rows_for((rows + qf::kMainRowsPerItem - 1) / qf::kMainRowsPerItem * t.panels);

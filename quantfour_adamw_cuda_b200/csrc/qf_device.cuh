@@ -14,6 +14,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -145,6 +146,37 @@ struct Elem<__nv_bfloat16> {
     }
 };
 
+// fp16 parameters and gradients (the reference's launcher dispatches half as well, optim/cuda_adamw_kernels.cu:443):
+// widened exactly, rounded to nearest even on the way back.  Tensors of this dtype always take the flat mapping.
+template <>
+struct Elem<__half> {
+    static __device__ __forceinline__ void load8(const char* base, int64_t e, float (&x)[8]) {
+        const uint4 r = *reinterpret_cast<const uint4*>(base + e * 2);
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+            x[2 * k] = f.x;
+            x[2 * k + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void store8(char* base, int64_t e, const float (&x)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const __half2 h = __floats2half2_rn(x[2 * k], x[2 * k + 1]);  // nearest even
+            w[k] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(base + e * 2) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    static __device__ __forceinline__ float load1(const char* base, int64_t e) {
+        return __half2float(reinterpret_cast<const __half*>(base)[e]);
+    }
+    static __device__ __forceinline__ void store1(char* base, int64_t e, float x) {
+        reinterpret_cast<__half*>(base)[e] = __float2half_rn(x);
+    }
+};
+
 // Eight elements as loaded, not yet widened: lets a loop fetch the next row before it works on this one.
 template <typename T>
 struct Raw8;
@@ -180,6 +212,24 @@ struct Raw8<__nv_bfloat16> {
             // byte permutes: a plain shift tends to be placed on the multiply-add pipe, which these kernels fill anyway
             asm("prmt.b32 %0, %1, 0, 0x1044;" : "=f"(x[2 * k]) : "r"(w[k]));
             asm("prmt.b32 %0, %1, 0, 0x3244;" : "=f"(x[2 * k + 1]) : "r"(w[k]));
+        }
+    }
+};
+
+template <>
+struct Raw8<__half> {
+    uint4 r;
+    __device__ __forceinline__ void from_shared(const char* arr, int lane) {
+        r = *reinterpret_cast<const uint4*>(arr + lane * 16);
+    }
+    __device__ __forceinline__ void load(const char* base, int64_t e) { r = *reinterpret_cast<const uint4*>(base + e * 2); }
+    __device__ __forceinline__ void widen(float (&x)[8]) const {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+            x[2 * k] = f.x;
+            x[2 * k + 1] = f.y;
         }
     }
 };

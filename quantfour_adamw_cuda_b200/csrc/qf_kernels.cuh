@@ -77,6 +77,8 @@ template <>
 __device__ __forceinline__ float round_as<float>(float x) { return x; }
 template <>
 __device__ __forceinline__ float round_as<__nv_bfloat16>(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+template <>
+__device__ __forceinline__ float round_as<__half>(float x) { return __half2float(__float2half_rn(x)); }
 struct HyperPack {
     HyperDev h[QF_MAX_HYPERS];
 };
@@ -1089,6 +1091,8 @@ step_pre_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restrict
         } else {
             if (t.dtype == QF_BF16)
                 pre_flat_rank1<__nv_bfloat16>(t, li, h, s, status);
+            else if (t.dtype == QF_F16)
+                pre_flat_rank1<__half>(t, li, h, s, status);
             else
                 pre_flat_rank1<float>(t, li, h, s, status);
         }
@@ -1140,6 +1144,8 @@ step_main_kernel(const DevTensor* __restrict__ tensors, const int64_t* __restric
         } else {
             if (tp->dtype == QF_BF16)
                 main_flat_dispatch<__nv_bfloat16>(tp, li, h, s, status, push);
+            else if (tp->dtype == QF_F16)
+                main_flat_dispatch<__half>(tp, li, h, s, status, push);
             else
                 main_flat_dispatch<float>(tp, li, h, s, status, push);
         }
@@ -1157,6 +1163,8 @@ single_tensor_kernel(const __grid_constant__ DevTensor t, const __grid_constant_
     if (item * (kPanelCols * kRowsPerItem) >= t.numel) return;
     if (t.dtype == QF_BF16)
         main_flat_dispatch<__nv_bfloat16>(&t, item, h, s, &g_unread_status, nullptr);
+    else if (t.dtype == QF_F16)
+        main_flat_dispatch<__half>(&t, item, h, s, &g_unread_status, nullptr);
     else
         main_flat_dispatch<float>(&t, item, h, s, &g_unread_status, nullptr);
 }

@@ -19,14 +19,14 @@ from . import _lib
 
 BLOCK = 128
 
-_DTYPES = {torch.float32: _lib.QF_F32, torch.bfloat16: _lib.QF_BF16}
+_DTYPES = {torch.float32: _lib.QF_F32, torch.bfloat16: _lib.QF_BF16, torch.float16: _lib.QF_F16}
 
 
 def _dtype_code(t: torch.Tensor) -> int:
     try:
         return _DTYPES[t.dtype]
     except KeyError:
-        raise TypeError(f"parameters must be float32 or bfloat16, got {t.dtype}") from None
+        raise TypeError(f"parameters must be float32, bfloat16 or float16, got {t.dtype}") from None
 
 
 def _need_cuda(*tensors: torch.Tensor) -> torch.device:

@@ -80,7 +80,8 @@ class FourBitAdamW(torch.optim.Optimizer):
     unsigned linear map without zero; for 2-D parameters the scale of element (i, j) is
     min(row_max[i], col_max[j]) (rank-1 normalisation), otherwise one scale per 128 elements.
     Parameters with at most ``quant_threshold`` elements keep float32 moments.  Parameters and
-    gradients must be CUDA tensors of dtype float32 or bfloat16.
+    gradients must be CUDA tensors of dtype float32 or bfloat16; float16 works as well, through the kernels' general
+    (slower) element mapping.
     """
 
     def __init__(
@@ -337,7 +338,7 @@ class FourBitAdamW(torch.optim.Optimizer):
                 if not p.is_contiguous():
                     raise RuntimeError("param must be contiguous")
                 if p.dtype not in _DTYPES:
-                    raise TypeError(f"parameters must be float32 or bfloat16, got {p.dtype}")
+                    raise TypeError(f"parameters must be float32, bfloat16 or float16, got {p.dtype}")
                 g = p.grad
                 if g.dtype != p.dtype or g.numel() != p.numel() or g.device != p.device:
                     raise RuntimeError("grad must match the parameter in dtype, numel and device")
@@ -524,7 +525,7 @@ class FourBitAdamW(torch.optim.Optimizer):
                 if not p.is_contiguous():
                     raise RuntimeError("param must be contiguous")
                 if p.dtype not in _DTYPES:
-                    raise TypeError(f"parameters must be float32 or bfloat16, got {p.dtype}")
+                    raise TypeError(f"parameters must be float32, bfloat16 or float16, got {p.dtype}")
                 g = p.grad
                 if g.dtype != p.dtype or g.numel() != p.numel() or g.device != p.device:
                     raise RuntimeError("grad must match the parameter in dtype, numel and device")

@@ -224,7 +224,7 @@ class CudaBackend:
         dev = states[0].p.device
         if dev.type != "cuda":
             raise RuntimeError("ShardedFourBitAdamW needs CUDA parameters; there is no CPU path")
-        dtype = _lib.QF_BF16 if states[0].p.dtype == torch.bfloat16 else _lib.QF_F32
+        dtype = {torch.bfloat16: _lib.QF_BF16, torch.float16: _lib.QF_F16}.get(states[0].p.dtype, _lib.QF_F32)
         descs = (_lib.QfTensorDesc * len(states))()
         for d, s in zip(descs, states):
             r = s.rec
@@ -301,7 +301,7 @@ class CudaBackend:
 class ShardedFourBitAdamW(torch.optim.Optimizer):
     """FourBitAdamW with ZeRO-1 style sharding of the 4-bit state over the ranks of `process_group`.
 
-    Same constructor arguments as FourBitAdamW.  All parameters must share one dtype (float32 or bfloat16)
+    Same constructor arguments as FourBitAdamW.  All parameters must share one dtype (float32, bfloat16 or float16)
     and one device, and every parameter must have a gradient at each step.  The parameters are moved into
     one flat buffer and become views of it.
 
@@ -342,8 +342,8 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
         p0 = self.params[0]
         if any(p.dtype != p0.dtype or p.device != p0.device for p in self.params):
             raise ValueError("all parameters must share dtype and device")
-        if p0.dtype not in (torch.float32, torch.bfloat16):
-            raise TypeError(f"parameters must be float32 or bfloat16, got {p0.dtype}")
+        if p0.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+            raise TypeError(f"parameters must be float32, bfloat16 or float16, got {p0.dtype}")
         self.layout = flat_layout([p.shape for p in self.params], self.world)
         self.step_count = 0
         if comm not in ("auto", "nccl", "p2p", "ce"):

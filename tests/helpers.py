@@ -13,7 +13,7 @@ from quantfour_adamw_cuda_b200 import _lib
 from quantfour_adamw_cuda_b200.optimizer import make_hyper
 
 KIND = {"fp32": _lib.QF_KIND_FP32, "block": _lib.QF_KIND_BLOCK, "rank1": _lib.QF_KIND_RANK1}
-DTYPE = {torch.float32: _lib.QF_F32, torch.bfloat16: _lib.QF_BF16}
+DTYPE = {torch.float32: _lib.QF_F32, torch.bfloat16: _lib.QF_BF16, torch.float16: _lib.QF_F16}
 
 
 class GpuState:

@@ -55,7 +55,7 @@ def _check_against_oracle(opt, params, cpu, states):
             assert torch.equal(vo["max1"].cpu(), st.v_scale)
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 def test_optimizer_matches_oracle_and_state_layout(dtype):
     model = _model(dtype)
     params = list(model.parameters())
@@ -172,7 +172,7 @@ def test_cpu_parameters_and_bad_dtypes_fail_loudly():
     p.grad = torch.randn_like(p)
     with pytest.raises(RuntimeError, match="no CPU path"):
         qf.FourBitAdamW([p]).step()
-    h = nn.Parameter(torch.randn(64, 128, device=DEV).half())
+    h = nn.Parameter(torch.randn(64, 128, device=DEV).double())
     h.grad = torch.randn_like(h)
     with pytest.raises(TypeError):
         qf.FourBitAdamW([h]).step()

@@ -69,7 +69,7 @@ def test_quantize_dequantize_rank1(shape):
     assert torch.equal(back.cpu(), CO.dequantize_rank1(oc, orow, ocol, *shape))
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("n", [1, 50, 4096, 5000])
 def test_fused_single_tensor_matches_oracle(dtype, n):
     p = (torch.randn(n) * 0.02).to(dtype)
@@ -82,7 +82,7 @@ def test_fused_single_tensor_matches_oracle(dtype, n):
         assert torch.equal(pg.cpu(), p) and torch.equal(mg.cpu(), st.m) and torch.equal(vg.cpu(), st.v)
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("n", [4097, 128 * 33, 100_003])
 def test_fused_4bit_matches_oracle(dtype, n):
     p = (torch.randn(n) * 0.02).to(dtype)
@@ -107,6 +107,7 @@ RAGGED = [
     ((5001,), torch.float32), ((4097,), torch.bfloat16), ((40, 50), torch.float32), ((1024,), torch.bfloat16),
     ((3, 5, 7, 99), torch.float32), ((1, 8192), torch.bfloat16), ((8192, 1), torch.float32), ((4096,), torch.float32),
     ((512, 768), torch.bfloat16), ((1,), torch.float32), ((48, 256), torch.float32),
+    ((96, 256), torch.float16), ((131, 77), torch.float16), ((6001,), torch.float16), ((100,), torch.float16),
 ]
 
 
