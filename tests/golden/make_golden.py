@@ -2,6 +2,7 @@
 
     python tests/golden/make_golden.py /path/to/reference          (all fixtures)
     python tests/golden/make_golden.py /path/to/reference nd       (scaling_nd.npz only)
+    python tests/golden/make_golden.py /path/to/reference qmaps    (qmaps_created.npz only)
 
 Needs the reference checkout (read-only) and no GPU.  The one reference module that holds the
 pure-PyTorch path creates a lookup table with ``device="cuda"`` at import time; it is loaded from
@@ -83,13 +84,29 @@ def nd_scaling(ref) -> None:
     np.savez(os.path.join(HERE, "scaling_nd.npz"), **out)
 
 
+def created_maps(root: str) -> None:
+    """The two 4-bit maps as the reference's generator makes them (optim/quant_opt_base.py:32-52: 'nonlinear' signed for
+    the first moment, 'power-1' unsigned for the second), beside the literals its kernels and its PyTorch path hard-code."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("quant_opt_base", os.path.join(root, "optim", "quant_opt_base.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    np.savez(os.path.join(HERE, "qmaps_created.npz"),
+             qm=mod.create_qmap("nonlinear", 4, True).numpy(), qv=mod.create_qmap("power-1", 4, False).numpy())
+
+
 def main(root: str, only: str = "") -> None:
+    if only == "qmaps":
+        created_maps(root)
+        print("wrote qmaps_created.npz")
+        return
     ref = load_reference(root)
     if only == "nd":
         nd_scaling(ref)
         print("wrote scaling_nd.npz")
         return
     nd_scaling(ref)
+    created_maps(root)
     np.savez(os.path.join(HERE, "tables.npz"),
              qm=ref._momentum_qmap.numpy(), mm=ref._momentum_midpoint_lut.numpy(),
              qv=ref._variance_qmap.numpy(), mv=ref._variance_midpoint_lut.numpy())
@@ -168,4 +185,4 @@ def main(root: str, only: str = "") -> None:
 if __name__ == "__main__":
     if len(sys.argv) not in (2, 3):
         raise SystemExit(__doc__)
-    main(*sys.argv[1:])     # a second argument "nd" writes scaling_nd.npz only
+    main(*sys.argv[1:])     # a second argument ("nd", "qmaps") writes that one fixture only

@@ -62,6 +62,20 @@ def test_scaling_helpers_match_reference():
     assert np.array_equal(xv.div(st).numpy(), z["xv_scaled"])
 
 
+def test_tables_against_the_maps_the_reference_generator_creates():
+    """qmaps_created.npz: create_qmap('nonlinear', 4, signed) and create_qmap('power-1', 4, unsigned) of the
+    reference (quant_opt_base.py:32-52).  The second-moment map is the hard-coded one bit for bit; the generated
+    first-moment map differs from the hard-coded literals at +-0.2125 and +-0.0325, each by one unit in the last place
+    (its linspace arithmetic lands on 0.21249999 and 0.032499999).  The kernels and this oracle follow the hard-coded
+    tables, as both of the reference's own paths do."""
+    z, t = _z("qmaps_created.npz"), _z("tables.npz")
+    assert np.array_equal(z["qv"], t["qv"]) and np.array_equal(TO.QV.numpy(), t["qv"])
+    differ = np.nonzero(z["qm"] != t["qm"])[0]
+    assert list(differ) == [3, 5, 9, 11]
+    assert np.array_equal(np.abs(z["qm"][differ] - t["qm"][differ]), np.spacing(np.abs(z["qm"][differ])))
+    assert np.array_equal(TO.QM.numpy(), t["qm"])
+
+
 def test_per_axis_scaling_of_tensors_with_more_than_two_axes_matches_reference():
     """scaling_nd.npz: the reference's variance_quant_scaling on a 3-D and a 4-D tensor (its per-axis maxima, the
     scaled tensor) and the scale tensor its dequantize side rebuilds from the maxima."""
