@@ -134,7 +134,7 @@ def measure(bench, workload: str, hp, args, dev, rank: int, world: int, detail: 
         for k in range(3):
             parts[k] += e[k].elapsed_time(e[k + 1]) / reps
     parts = [_max_over_ranks(x, dev) for x in parts]
-    reduce_ms = None
+    reduce_ms = nccl_reduce_ms = None
     if reduce_grads:
         reduce_ms = 0.0
         for _ in range(reps):
@@ -145,6 +145,21 @@ def measure(bench, workload: str, hp, args, dev, rank: int, world: int, detail: 
             torch.cuda.synchronize(dev)
             reduce_ms += e[0].elapsed_time(e[1]) / reps
         reduce_ms = _max_over_ranks(reduce_ms, dev)
+        # the yardstick: NCCL's reduce-scatter of the same bytes (what the optimizer falls back to without peer mappings)
+        nccl_reduce_ms = None
+        if opt.grad_deltas:
+            saved, opt.grad_deltas = opt.grad_deltas, []
+            nccl_reduce_ms = 0.0
+            for i in range(reps + 1):
+                dist.barrier()
+                e[0].record()
+                opt._reduce_gradients()
+                e[1].record()
+                torch.cuda.synchronize(dev)
+                if i:
+                    nccl_reduce_ms += e[0].elapsed_time(e[1]) / reps
+            nccl_reduce_ms = _max_over_ranks(nccl_reduce_ms, dev)
+            opt.grad_deltas = saved
     push_ms = None
     if opt.comm in ("p2p", "ce"):   # the main pass with the delivery inside it (peer stores, or pieces + copy engines), closed by the small collective
         push_ms = 0.0
@@ -217,7 +232,7 @@ def measure(bench, workload: str, hp, args, dev, rank: int, world: int, detail: 
         del host, e2e_step
 
     out = {"workload": workload, "tensors": len(shapes), "params": n_params, "alg_bytes": alg_bytes, "ms_per_step": ms_per_step,
-           "warm": warm, "parts": parts, "reduce_ms": reduce_ms, "push_ms": push_ms, "comm": opt.comm_selected,
+           "warm": warm, "parts": parts, "reduce_ms": reduce_ms, "nccl_reduce_ms": nccl_reduce_ms, "push_ms": push_ms, "comm": opt.comm_selected,
            "shard_elements": lay.shard, "flat_total": lay.total, "replicas_identical": replicas_identical,
            "oracle_subset": oracle_subset, "launches_per_step": launches_per_step, "clocks": clocks, "e2e": e2e,
            "reduce_grads": reduce_grads}
@@ -281,7 +296,7 @@ def run(args, hp) -> None:
                          "note": "per rank: algorithmic bytes of the rank's shard over the device time of its fused step "
                                  "(both halves incl. the max exchange), delivery of the parameters excluded",
                          "parts_ms": {"pre+max_exchange": parts[0], "main": parts[1], "all_gather": parts[2],
-                                      "grad_reduce_scatter": m["reduce_ms"]},
+                                      "grad_reduce_scatter": m["reduce_ms"], "grad_reduce_scatter_nccl": m["nccl_reduce_ms"]},
                          "all_gather": {"bytes_received_per_gpu": gather_bytes,
                                         "GBps_per_gpu": gather_bytes / (parts[2] * 1e-3) / 1e9 if parts[2] else None},
                          "main_with_delivery": None if push_ms is None else {

@@ -239,6 +239,21 @@ int qf_peer_close(void* base, int device);
  */
 int qf_peer_copy(void* dst, int dst_device, const void* src, size_t bytes, int device, void* stream);
 
+/*
+ * The gradient half of a sharded step without a library collective: the device that owns a range of the flat gradient
+ * buffer takes the mean of all devices' copies of that range through peer loads and writes it over its own copy:
+ *     g[i] := RN((copy_0[i] + copy_1[i] + ... ) * inv_count)      sum in fp32, in the order given, rounded to `dtype`
+ * copy_delta_bytes[k] = (address of copy k's range as mapped in this process, qf_peer_open) - g; 0 names this device's
+ * own copy, which must be among them; at most QF_MAX_PEERS copies.  Only g[0 .. numel) is written, and nothing else
+ * of any copy is read, so all devices can run their call at the same time as long as their ranges are disjoint.  The
+ * caller makes sure that every device's gradients are complete before any call starts (one small collective) and that
+ * no device overwrites its gradients before all calls have finished (any later collective of the step).  Measured on
+ * two B200s, 13B shape: see the design notes; NCCL's reduce-scatter of the same bytes is the yardstick.  No counterpart
+ * in the reference (it has no sharding).
+ */
+int qf_grad_mean_peers(void* g, int64_t numel, int dtype, const int64_t* copy_delta_bytes, int n_copies,
+                       float inv_count, int device, void* stream);
+
 /* Synchronise `stream`, read the status word kept in `workspace` into *status (QF_STATUS_* bits)
  * and clear it. */
 int qf_read_status(void* workspace, int device, void* stream, uint32_t* status);

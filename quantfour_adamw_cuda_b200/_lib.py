@@ -60,6 +60,7 @@ _SIGNATURES = {
     "qf_peer_open": (C.c_int, [C.c_char_p, C.c_int, C.POINTER(C.c_void_p)]),
     "qf_peer_close": (C.c_int, [C.c_void_p, C.c_int]),
     "qf_peer_copy": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]),
+    "qf_grad_mean_peers": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.POINTER(C.c_int64), C.c_int, C.c_float, C.c_int, C.c_void_p]),
     "qf_read_status": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.POINTER(C.c_uint32)]),
     "qf_release_workspace": (C.c_int, [C.c_void_p, C.c_int]),
     "qf_read_status_noalloc": (C.c_int, [C.c_int, C.c_void_p, C.POINTER(C.c_uint32)]),

@@ -1,5 +1,6 @@
 // Host side of libquantfour_b200.so: argument validation, the device descriptor table and the
 // launches.  The exported functions are declared and documented in include/quantfour_b200.h.
+#include <algorithm>
 #include <cmath>
 #include <cstdarg>
 #include <cstddef>
@@ -625,6 +626,39 @@ int qf_peer_copy(void* dst, int dst_device, const void* src, size_t bytes, int d
         QF_CUDA(cudaMemcpyPeerAsync(dst, dst_device, src, device, bytes, static_cast<cudaStream_t>(stream)));
     else
         QF_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)));
+    return QF_OK;
+}
+
+int qf_grad_mean_peers(void* g, int64_t numel, int dtype, const int64_t* copy_delta_bytes, int n_copies, float inv_count,
+                       int device, void* stream) {
+    g_err[0] = 0;
+    if (numel < 0) return fail(QF_ERR_BAD_ARG, "qf_grad_mean_peers: negative numel");
+    if (numel == 0) return QF_OK;
+    if (!g || !copy_delta_bytes) return fail(QF_ERR_BAD_ARG, "qf_grad_mean_peers: null pointer");
+    if (!valid_dtype(dtype)) return fail(QF_ERR_BAD_ARG, "bad dtype %d", dtype);
+    if (n_copies < 1 || n_copies > QF_MAX_PEERS)
+        return fail(QF_ERR_BAD_ARG, "qf_grad_mean_peers: n_copies must be in 1..%d, got %d", QF_MAX_PEERS, n_copies);
+    if (!aligned(g, 16)) return fail(QF_ERR_BAD_ARG, "qf_grad_mean_peers: the range must start on a 16-byte boundary");
+    qf::PushPack pp;
+    memset(&pp, 0, sizeof pp);
+    pp.n = n_copies;
+    for (int k = 0; k < n_copies; ++k) {
+        if (copy_delta_bytes[k] % 16) return fail(QF_ERR_BAD_ARG, "copy %d: the distance to the copy must be a multiple of 16 bytes", k);
+        pp.delta[k] = copy_delta_bytes[k];
+    }
+    QF_CUDA(cudaSetDevice(device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t turns = (numel + 15) / 16;     // a thread takes two 8-element vectors per turn
+    const int64_t want = (turns + qf::kThreads - 1) / qf::kThreads;
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(want, static_cast<int64_t>(sm_count()) * 32));
+    char* gp = static_cast<char*>(g);
+    if (dtype == QF_BF16)
+        qf::grad_mean_peers_kernel<__nv_bfloat16><<<grid, qf::kThreads, 0, st>>>(gp, numel, pp, inv_count);
+    else if (dtype == QF_F16)
+        qf::grad_mean_peers_kernel<__half><<<grid, qf::kThreads, 0, st>>>(gp, numel, pp, inv_count);
+    else
+        qf::grad_mean_peers_kernel<float><<<grid, qf::kThreads, 0, st>>>(gp, numel, pp, inv_count);
+    QF_CUDA(cudaGetLastError());
     return QF_OK;
 }
 

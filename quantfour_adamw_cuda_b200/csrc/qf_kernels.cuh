@@ -1169,6 +1169,49 @@ single_tensor_kernel(const __grid_constant__ DevTensor t, const __grid_constant_
         main_flat_dispatch<float>(&t, item, h, s, &g_unread_status, nullptr);
 }
 
+// Mean of the copies of a gradient range that the devices of a node hold, taken by the device that owns the range (the
+// gradient half of a sharded step): g[i] := RN((copy_0[i] + copy_1[i] + ...) * inv_count) in the gradient's dtype, the
+// sum in fp32 in the order of `pp.delta` (byte distances from g to each copy; 0 = this device's own).  Every thread has
+// one 16-byte load per copy in flight, so the peer links are busy from all warps at once; only this device's copy is
+// written, and only inside the range, which no other device reads.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+grad_mean_peers_kernel(char* __restrict__ g, int64_t numel, const __grid_constant__ PushPack pp, float inv_count) {
+    constexpr int64_t kVec = 8;
+    const int64_t nvec = numel / kVec, npair = nvec / 2;
+    const int n = pp.n;
+    // two neighbouring vectors per thread and turn: all loads of a copy go out before the first sum needs one
+    for (int64_t q = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; q < npair; q += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t e = q * 2 * kVec;
+        float a0[8], a1[8], x0[8], x1[8];
+        Elem<T>::load8(g + pp.delta[0], e, a0);
+        Elem<T>::load8(g + pp.delta[0], e + kVec, a1);
+        for (int k = 1; k < n; ++k) {
+            Elem<T>::load8(g + pp.delta[k], e, x0);
+            Elem<T>::load8(g + pp.delta[k], e + kVec, x1);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                a0[i] = __fadd_rn(a0[i], x0[i]);
+                a1[i] = __fadd_rn(a1[i], x1[i]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            a0[i] = __fmul_rn(a0[i], inv_count);
+            a1[i] = __fmul_rn(a1[i], inv_count);
+        }
+        Elem<T>::store8(g, e, a0);
+        Elem<T>::store8(g, e + kVec, a1);
+    }
+    if (blockIdx.x == 0) {     // what two-vector turns leave over: at most 15 elements
+        for (int64_t e = npair * 2 * kVec + threadIdx.x; e < numel; e += blockDim.x) {
+            float a = Elem<T>::load1(g + pp.delta[0], e);
+            for (int k = 1; k < n; ++k) a = __fadd_rn(a, Elem<T>::load1(g + pp.delta[k], e));
+            Elem<T>::store1(g, e, __fmul_rn(a, inv_count));
+        }
+    }
+}
+
 // End of a step that took its hyper-parameters from a device-resident table: the next step takes the next row.
 // counters[0] stops one past the last row; a step that ran there used the last row again, which is an error
 // (reported in the status word) unless the caller said that the last row repeats for ever.

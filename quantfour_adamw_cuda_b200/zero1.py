@@ -351,6 +351,7 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
         self._flatten()
         self._build_state()
         self.reduce_grads = bool(reduce_grads)
+        self.grad_deltas: List[int] = []      # byte distances to every rank's gradient buffer (peer mappings), or empty
         self.flat_grad: Optional[torch.Tensor] = None
         if self.reduce_grads:
             self.flat_grad = torch.zeros_like(self.flat)
@@ -403,7 +404,20 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
         if not (self.sharded and self.world > 1):
             return
         lo, hi = self.layout.range_of(self.rank)
-        if self.flat_grad.is_cuda:
+        if self.grad_deltas:
+            # this rank reads its range of every rank's gradients through peer loads and writes the mean over its own
+            # copy (fp32 sum in rank order, one rounding).  The collective in front makes every rank's gradients
+            # complete before anyone reads them; the next collective of the step (the exchange of maxima, the token
+            # around the peer stores, the all-gather) keeps every rank from touching its gradients again before all
+            # ranks' reads have finished.
+            dist.all_reduce(self._token, op=dist.ReduceOp.MAX, group=self.group)
+            dev = self.flat_grad.device
+            arr = (C.c_int64 * len(self.grad_deltas))(*self.grad_deltas)
+            dtype = {torch.bfloat16: _lib.QF_BF16, torch.float16: _lib.QF_F16}.get(self.flat_grad.dtype, _lib.QF_F32)
+            _lib.check(_lib.lib().qf_grad_mean_peers(C.c_void_p(self.flat_grad[lo:hi].data_ptr()), hi - lo, dtype, arr, len(arr),
+                                                     1.0 / self.world, dev.index,
+                                                     C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)), "qf_grad_mean_peers")
+        elif self.flat_grad.is_cuda:
             dist.reduce_scatter_tensor(self.flat_grad[lo:hi], self.flat_grad, op=dist.ReduceOp.AVG, group=self.group)
         else:  # CPU process groups (tests)
             dist.all_reduce(self.flat_grad, op=dist.ReduceOp.SUM, group=self.group)
@@ -466,6 +480,8 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
         err, mine = "", None
         try:
             mine = self.backend.export_buffer(self.flat) + (socket.gethostname(), str(torch.cuda.get_device_properties(dev).uuid))
+            if self.reduce_grads:     # the gradient buffers are shared the same way: the reduction reads them through peer loads
+                mine = mine + self.backend.export_buffer(self.flat_grad)
         except Exception as e:  # noqa: BLE001 - any failure means: no peer path
             err = f"{type(e).__name__}: {e}"
         everyone: List[Any] = [None] * self.world
@@ -479,11 +495,22 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
                 # copies of a piece -- then targets a different GPU on every rank at any moment
                 for k in range(1, self.world):
                     r = (self.rank + k) % self.world
-                    handle, off, _, uuid = everyone[r]
+                    handle, off, _, uuid = everyone[r][:4]
                     base, addr = self.backend.open_buffer(handle, off, dev)
                     self._peer_bases.append(base)
                     self.peer_deltas.append(addr - self.flat.data_ptr())
                     self.peer_devices.append(visible.get(uuid, -1))   # the peer's GPU as this process numbers it
+                if self.reduce_grads:
+                    # every rank's gradient buffer, in rank order (0 = this rank's own): the order of the sum
+                    deltas = []
+                    for r in range(self.world):
+                        if r == self.rank:
+                            deltas.append(0)
+                            continue
+                        base, addr = self.backend.open_buffer(everyone[r][4], everyone[r][5], dev)
+                        self._peer_bases.append(base)
+                        deltas.append(addr - self.flat_grad.data_ptr())
+                    self.grad_deltas = deltas
             except Exception as e:  # noqa: BLE001
                 err = f"{type(e).__name__}: {e}"
         elif not err:
@@ -547,6 +574,7 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
             except Exception:  # noqa: BLE001 - shutting down
                 pass
         self._peer_bases, self.peer_deltas, self.peer_devices, self.comm = [], [], [], "nccl"
+        self.grad_deltas = []
 
     def __del__(self):
         try:    # peer mappings must not outlive the optimizer; explicit close() stays the orderly way

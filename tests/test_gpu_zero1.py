@@ -130,6 +130,37 @@ def test_emulated_ranks_with_pipelined_copies(world, dtype):
             assert torch.equal(p.detach().cpu(), w), f"tensor {i} {SHAPES[i]} differs in {(p.detach().cpu() != w).sum()} places"
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("copies,n", [(2, 1 << 16), (4, 100_003), (7, 12_345)])
+def test_gradient_mean_over_copies_is_the_fp32_sum_in_the_given_order_rounded_once(dtype, copies, n):
+    """qf_grad_mean_peers with the other ranks' gradient buffers standing in as plain buffers of the same device: the
+    owner's range becomes RN((g_0 + g_1 + ...) / copies), summed in fp32 in the order of the list; nothing outside the
+    range and nothing of the other copies is written."""
+    import ctypes as C
+    from quantfour_adamw_cuda_b200 import _lib
+    gen = torch.Generator().manual_seed(copies * 131 + n)
+    pad = 64
+    bufs = [(torch.randn(n + 2 * pad, generator=gen) * 1e-2).to(dtype).cuda() for _ in range(copies)]
+    before = [b.clone() for b in bufs]
+    own = 1 % copies                                     # the owner is not the first of the list
+    order = list(range(copies))
+    acc = before[order[0]][pad:pad + n].float()
+    for k in order[1:]:
+        acc = acc + before[k][pad:pad + n].float()
+    want = (acc * torch.tensor(1.0 / copies, dtype=torch.float32)).to(dtype)
+    g = bufs[own][pad:pad + n]
+    deltas = (C.c_int64 * copies)(*[bufs[k].data_ptr() - bufs[own].data_ptr() for k in order])
+    code = {torch.float32: _lib.QF_F32, torch.bfloat16: _lib.QF_BF16, torch.float16: _lib.QF_F16}[dtype]
+    _lib.check(_lib.lib().qf_grad_mean_peers(C.c_void_p(g.data_ptr()), n, code, deltas, copies, 1.0 / copies, 0,
+                                             C.c_void_p(torch.cuda.current_stream().cuda_stream)), "qf_grad_mean_peers")
+    torch.cuda.synchronize()
+    assert torch.equal(g, want.cuda())
+    for k in range(copies):
+        if k != own:
+            assert torch.equal(bufs[k], before[k])
+    assert torch.equal(bufs[own][:pad], before[own][:pad]) and torch.equal(bufs[own][pad + n:], before[own][pad + n:])
+
+
 def test_push_rejects_bad_peers():
     params = [torch.nn.Parameter(torch.zeros(64, 256, device="cuda"))]
     opt = ShardedFourBitAdamW(params, lr=1e-3)

@@ -163,3 +163,17 @@ def test_general_step_call_validates_what_it_is_asked_to_do(lib):
     assert lib.qf_step_run(*args, _lib.QF_RUN_PRE, deltas, 1) == 1 and b"second half" in lib.qf_last_error()
     assert lib.qf_step_run(*args, _lib.QF_RUN_MAIN | _lib.QF_RUN_RELAXED_UPDATE, deltas, 1) == 1 and b"relaxed" in lib.qf_last_error()
     assert lib.qf_step_run(*args, _lib.QF_RUN_MAIN, None, 1) == 1 and b"peer_delta_bytes" in lib.qf_last_error()
+
+
+def test_gradient_mean_validates_its_arguments_before_touching_a_device(lib):
+    A = 0x10000     # never dereferenced
+    d = (C.c_int64 * 2)(0, 4096)
+    assert lib.qf_grad_mean_peers(A, -1, _lib.QF_BF16, d, 2, 0.5, 0, None) == 1 and b"negative" in lib.qf_last_error()
+    assert lib.qf_grad_mean_peers(A, 0, _lib.QF_BF16, d, 2, 0.5, 0, None) == 0
+    assert lib.qf_grad_mean_peers(None, 8, _lib.QF_BF16, d, 2, 0.5, 0, None) == 1 and b"null" in lib.qf_last_error()
+    assert lib.qf_grad_mean_peers(A, 8, 7, d, 2, 0.5, 0, None) == 1 and b"dtype" in lib.qf_last_error()
+    assert lib.qf_grad_mean_peers(A, 8, _lib.QF_BF16, d, 0, 0.5, 0, None) == 1 and b"n_copies" in lib.qf_last_error()
+    assert lib.qf_grad_mean_peers(A, 8, _lib.QF_BF16, d, 99, 0.5, 0, None) == 1 and b"n_copies" in lib.qf_last_error()
+    assert lib.qf_grad_mean_peers(A + 2, 8, _lib.QF_BF16, d, 2, 0.5, 0, None) == 1 and b"16-byte" in lib.qf_last_error()
+    bad = (C.c_int64 * 2)(0, 4100)
+    assert lib.qf_grad_mean_peers(A, 8, _lib.QF_BF16, bad, 2, 0.5, 0, None) == 1 and b"multiple of 16" in lib.qf_last_error()
