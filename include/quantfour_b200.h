@@ -248,8 +248,8 @@ int qf_peer_copy(void* dst, int dst_device, const void* src, size_t bytes, int d
  * of any copy is read, so all devices can run their call at the same time as long as their ranges are disjoint.  The
  * caller makes sure that every device's gradients are complete before any call starts (one small collective) and that
  * no device overwrites its gradients before all calls have finished (any later collective of the step).  Measured on
- * two B200s, 13B shape: see the design notes; NCCL's reduce-scatter of the same bytes is the yardstick.  No counterpart
- * in the reference (it has no sharding).
+ * two B200s, 13 G bf16 gradients: 21.0 ms (620 GB/s of peer loads per device) against 26.4 ms for NCCL's reduce-scatter
+ * of the same bytes.  No counterpart in the reference (it has no sharding).
  */
 int qf_grad_mean_peers(void* g, int64_t numel, int dtype, const int64_t* copy_delta_bytes, int n_copies,
                        float inv_count, int device, void* stream);

@@ -174,8 +174,8 @@ __global__ void k_dequant_v(uint32_t lo, uint64_t count, Report* r) {
 // ---- dispatch probe ------------------------------------------------------------------------------------------
 // How many cycles an SM sub-partition needs per warp instruction of a class, alone and mixed 1 : 1 with packed FMAs:
 // NF independent packed FMAs and NA independent instructions of class KIND (0 lop3, 1 prmt, 2 funnel shift, 3 integer
-// multiply-add, 4 scalar fma) per group, four warps per sub-partition.  The design notes quote these figures for the
-// statement that the step kernels are bound by instruction dispatch.
+// multiply-add, 4 scalar fma) per group, four warps per sub-partition: the yardstick behind the statement that the step
+// kernels are bound by instruction dispatch.
 template <int NF, int NA, int KIND>
 __global__ void __launch_bounds__(256) k_probe(float2* out, unsigned* iout, int iters, float2 a, float2 b, unsigned k) {
     float2 f[8];
