@@ -108,6 +108,8 @@ RAGGED = [
     ((3, 5, 7, 99), torch.float32), ((1, 8192), torch.bfloat16), ((8192, 1), torch.float32), ((4096,), torch.float32),
     ((512, 768), torch.bfloat16), ((1,), torch.float32), ((48, 256), torch.float32),
     ((96, 256), torch.float16), ((131, 77), torch.float16), ((6001,), torch.float16), ((100,), torch.float16),
+    # panel tensors whose row count is odd or not a multiple of the item length: the last row of an item goes alone
+    ((77, 256), torch.bfloat16), ((17, 512), torch.float32), ((131, 768), torch.bfloat16),
 ]
 
 
