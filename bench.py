@@ -161,7 +161,7 @@ def run_cpu(workload: str, form: str, steps: int, warmup: int, budget_s: float =
 def reference_arm(args):
     if int(os.environ.get("RANK", "0")) != 0:
         return
-    workload = args.workload or ("llama7b" if args.gpus == 1 else "llama13b")
+    workload = args.workload or "llama7b"     # the same workload as the main arm, at every N
     value, cores, dt, text = run_cpu(workload, "torch", args.steps, args.warmup, budget_s=120.0)
     print(json.dumps({
         "impl": "reference", "metric": "4-bit AdamW step throughput", "value": value, "unit": "Gparams/s",
