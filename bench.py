@@ -3,11 +3,11 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-One "step" is one optimizer step over the whole parameter list of the workload.  At N = 1 the
-workload is the Llama-7B-shaped parameter set (bf16 parameters and gradients, per-tensor gradient
-sigma log-uniform in [1e-5, 1e-2], 0.1 % of entries x100); at N > 1 the Llama-13B-shaped set with the
-optimizer state sharded over the ranks and an all-gather of the updated parameters.  All data is
-synthetic and seeded.  Rank 0 prints one JSON line.
+One "step" is one optimizer step over the whole parameter list of the workload: at every N the
+Llama-7B-shaped parameter set (bf16 parameters and gradients, per-tensor gradient sigma log-uniform in
+[1e-5, 1e-2], 0.1 % of entries x100); at N > 1 the optimizer state is sharded over the ranks and the updated
+parameters are delivered to every rank inside the step (the Llama-13B-shaped set runs beside it, under `also`).
+All data is synthetic and seeded.  Rank 0 prints one JSON line.
 
 `value`      Gparams/s with everything resident in HBM, device time over exactly K steps.
 `e2e`        the same metric through the public optimizer class with the step's input (the gradients)
