@@ -517,7 +517,8 @@ def main():
                     help="N=1: set every step counter to this value after the warm-up (>= 20000 shows the late-training "
                          "regime where sqrt(1 - beta2^t) has rounded to 1)")
     ap.add_argument("--reduce-grads", action="store_true",
-                    help="N>1: the step starts with a reduce-scatter (mean) of per-rank gradients kept in a flat buffer")
+                    help="N>1: the step starts with the mean of the per-rank gradients kept in a flat buffer, each rank over its own range "
+                         "(peer loads inside a node, NCCL's reduce-scatter timed beside it)")
     ap.add_argument("--grad-scale", type=float, default=None,
                     help="N=1: pass this factor to every timed step (the first pass then rewrites the gradients scaled); "
                          "use a value next to 1, e.g. 1.0000001, so that repeated steps do not drive the data to zero")
