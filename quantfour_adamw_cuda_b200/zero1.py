@@ -307,8 +307,9 @@ class ShardedFourBitAdamW(torch.optim.Optimizer):
 
     `reduce_grads=True` adds the other half of ZeRO-1: the gradients live in a flat buffer of the same layout
     (every `p.grad` is a view of it, so backward accumulates in place), the ranks hold different gradients,
-    and each step starts with a reduce-scatter that leaves the mean over the ranks of this rank's range where
-    the step reads it.  Without it (default) the caller has already made the gradients equal on all ranks.
+    and each step starts by leaving the mean over the ranks of this rank's range where the step reads it: inside a
+    node through the library's own kernel (qf_grad_mean_peers: peer loads, fp32 sum in rank order, one rounding),
+    otherwise through NCCL's reduce-scatter.  Without it (default) the caller has already made the gradients equal on all ranks.
     """
 
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, *, fused: Optional[bool] = False,
